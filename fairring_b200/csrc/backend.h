@@ -1,0 +1,201 @@
+// The c10d backend: what `torch.distributed.init_process_group("fairring")`
+// talks to.  Counterpart of ProcessGroupFairring / WorkFairring /
+// OptionsFairring in the reference (fairring/process_group.{h,cc}), rebuilt on
+// today's c10d::Backend / c10d::Work interfaces.
+//
+//   own algorithms : allreduce, reduce_scatter, _reduce_scatter_base,
+//                    allgather, _allgather_base  (CUDA tensors -> Engine,
+//                    CPU tensors -> CpuEngine)
+//   delegated      : everything else, to a lazily created NCCL (CUDA) or Gloo
+//                    (CPU) backend on a prefixed store; also any reduction op
+//                    or dtype the kernels do not cover, instead of aborting
+//                    the process as the reference does (fairring/utils.h:247-256).
+#pragma once
+
+#include <torch/csrc/distributed/c10d/Backend.hpp>
+#include <torch/csrc/distributed/c10d/Store.hpp>
+#include <torch/csrc/distributed/c10d/Work.hpp>
+
+#include <functional>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+
+#include "cpu_path.h"
+#include "engine.h"
+#include "topology.h"
+
+namespace fairring {
+
+constexpr const char* kBackendName = "fairring";
+
+struct OptionsFairring : c10d::Backend::Options {
+  explicit OptionsFairring(std::chrono::milliseconds timeout = kBackendDefaultTimeout)
+      : c10d::Backend::Options(kBackendName, timeout) {}
+
+  // Same three knobs as the reference (fairring/process_group.h:52-77) ...
+  int64_t max_memory_allocated_in_bytes = 50ll << 20;
+  int64_t max_padding_allocated_in_bytes = 1 << 20;  // accepted; tails are predicated, no padding buffers exist
+  int64_t min_parallelism = 16;
+  bool is_high_priority_stream = true;
+  // ... plus what the B200 design adds.
+  int64_t slice_size_in_bytes = 25ll << 20;
+  int64_t gpus_per_machine = 0;   // 0: one group per real host
+  bool favorable_layout = false;  // numbering of virtual machines: d*M+m instead of m*D+d
+  std::string algo = "auto";
+  int64_t blocks = 32;
+  int64_t oneshot_max_bytes = 256 << 10;
+  int64_t nvls_min_bytes = 0;
+  int64_t nvls_oneshot_max_bytes = 2 << 20;
+  int64_t device_timeout_ms = 30000;
+  std::string nvls = "auto";       // auto | on | off
+  std::string transport = "auto";  // auto | vmm | ipc
+  bool command_thread = false;
+  bool blocking_wait = false;
+  std::string boot_id_override;    // tests: pretend to be on another host
+};
+
+class BackendFairring;
+
+class WorkFairring : public c10d::Work {
+ public:
+  WorkFairring(c10d::OpType op, c10::intrusive_ptr<c10::ivalue::Future> future,
+               std::shared_ptr<Engine> engine, bool blocking,
+               std::chrono::milliseconds default_timeout);
+  bool isCompleted() override;
+  bool isSuccess() const override;
+  std::exception_ptr exception() const override;
+  std::vector<at::Tensor> result() override;
+  void synchronize() override;
+  bool wait(std::chrono::milliseconds timeout = kNoTimeout) override;
+  void abort() override;
+  c10::intrusive_ptr<c10::ivalue::Future> getFuture() override;
+
+  // Set by the enqueueing code once the completion event has been recorded.
+  void setDoneEvent(cudaEvent_t e, int device);
+
+ private:
+  c10::intrusive_ptr<c10::ivalue::Future> future_;
+  std::shared_ptr<Engine> engine_;
+  bool blocking_;
+  std::chrono::milliseconds default_timeout_;
+  std::atomic<cudaEvent_t> done_{nullptr};
+  int device_ = -1;
+};
+
+using DelegateFactory = std::function<c10::intrusive_ptr<c10d::Backend>(const std::string&)>;
+
+class BackendFairring : public c10d::Backend {
+ public:
+  BackendFairring(c10::intrusive_ptr<c10d::Store> store, int rank, int size,
+                  c10::intrusive_ptr<OptionsFairring> options);
+  ~BackendFairring() override;
+
+  const std::string getBackendName() const override { return kBackendName; }
+  c10::intrusive_ptr<c10d::Backend::Options> getBackendOptions() override { return options_; }
+
+  // --- own algorithms -------------------------------------------------------
+  c10::intrusive_ptr<c10d::Work> allreduce(std::vector<at::Tensor>& tensors,
+                                           const c10d::AllreduceOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> allgather(std::vector<std::vector<at::Tensor>>& outputs,
+                                           std::vector<at::Tensor>& inputs,
+                                           const c10d::AllgatherOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> _allgather_base(at::Tensor& output, at::Tensor& input,
+                                                 const c10d::AllgatherOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> reduce_scatter(std::vector<at::Tensor>& outputs,
+                                                std::vector<std::vector<at::Tensor>>& inputs,
+                                                const c10d::ReduceScatterOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> _reduce_scatter_base(at::Tensor& output, at::Tensor& input,
+                                                      const c10d::ReduceScatterOptions& opts) override;
+  // all_reduce with the gradient scale and the wire-dtype cast fused into the
+  // kernels (what the DDP communication hook calls).
+  c10::intrusive_ptr<c10d::Work> allreduceFused(at::Tensor tensor, double scale,
+                                                c10::optional<at::ScalarType> wire_dtype,
+                                                const std::string& op);
+
+  // --- delegated --------------------------------------------------------------
+  c10::intrusive_ptr<c10d::Work> broadcast(std::vector<at::Tensor>& t,
+                                           const c10d::BroadcastOptions& o) override;
+  c10::intrusive_ptr<c10d::Work> allreduce_coalesced(std::vector<at::Tensor>& t,
+                                                     const c10d::AllreduceCoalescedOptions& o) override;
+  c10::intrusive_ptr<c10d::Work> reduce(std::vector<at::Tensor>& t,
+                                        const c10d::ReduceOptions& o) override;
+  c10::intrusive_ptr<c10d::Work> allgather_coalesced(std::vector<std::vector<at::Tensor>>& o,
+                                                     std::vector<at::Tensor>& i,
+                                                     const c10d::AllgatherOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> allgather_into_tensor_coalesced(
+      std::vector<at::Tensor>& o, std::vector<at::Tensor>& i,
+      const c10d::AllgatherOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> reduce_scatter_tensor_coalesced(
+      std::vector<at::Tensor>& o, std::vector<at::Tensor>& i,
+      const c10d::ReduceScatterOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> gather(std::vector<std::vector<at::Tensor>>& o,
+                                        std::vector<at::Tensor>& i,
+                                        const c10d::GatherOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> scatter(std::vector<at::Tensor>& o,
+                                         std::vector<std::vector<at::Tensor>>& i,
+                                         const c10d::ScatterOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> alltoall_base(at::Tensor& o, at::Tensor& i,
+                                               std::vector<int64_t>& os, std::vector<int64_t>& is,
+                                               const c10d::AllToAllOptions& opts) override;
+  c10::intrusive_ptr<c10d::Work> alltoall(std::vector<at::Tensor>& o, std::vector<at::Tensor>& i,
+                                          const c10d::AllToAllOptions& opts) override;
+  void monitoredBarrier(const c10d::BarrierOptions& o, bool wait_all_ranks) override;
+  c10::intrusive_ptr<c10d::Work> send(std::vector<at::Tensor>& t, int dst, int tag) override;
+  c10::intrusive_ptr<c10d::Work> recv(std::vector<at::Tensor>& t, int src, int tag) override;
+  c10::intrusive_ptr<c10d::Work> recvAnysource(std::vector<at::Tensor>& t, int tag) override;
+  c10::intrusive_ptr<c10d::Work> barrier(const c10d::BarrierOptions& o) override;
+
+  void setSequenceNumberForGroup() override {}
+  uint64_t getSequenceNumberForGroup() override { return seq_; }
+  void setTimeout(std::chrono::milliseconds t) override { options_->timeout = t; }
+  c10d::ErrorType getError() override;
+  void abort() override;
+  void shutdown() override;
+
+  // --- introspection and control (Python) ------------------------------------
+  void setDelegateFactory(DelegateFactory f) { factory_ = std::move(f); }
+  std::string describe();
+  std::map<std::string, int64_t> stats();
+  void checkHealth();
+  void reset();
+  void skipCpuSignals(int n);
+  std::map<std::string, int64_t> deployment();
+
+ private:
+  enum class Route { OWN_GPU, OWN_CPU, DELEGATE };
+  struct Mapped {
+    bool ok = false;
+    DType dtype = DType::F32;
+    RedOp op = RedOp::SUM;
+    float scale = 1.0f;
+  };
+  Mapped mapOp(const at::Tensor& t, const c10d::ReduceOp& op) const;
+  Route routeFor(const at::Tensor& t, bool mapped_ok);
+  c10::intrusive_ptr<c10d::Backend> delegate(const at::Device& dev);
+  c10::intrusive_ptr<c10d::Backend> delegateFor(const std::vector<at::Tensor>& t);
+  const Deployment& ensureDeployment();
+  std::shared_ptr<Engine> ensureEngine(int device);
+  CpuEngine& ensureCpuEngine();
+  c10::intrusive_ptr<c10d::Work> runGpu(c10d::OpType type, const CollectiveDesc& d,
+                                        std::vector<at::Tensor> keep,
+                                        std::vector<at::Tensor> result,
+                                        std::function<void()> epilogue);
+  c10::intrusive_ptr<c10d::Work> completedWork(c10d::OpType type, std::vector<at::Tensor> result);
+
+  c10::intrusive_ptr<c10d::Store> store_;
+  c10::intrusive_ptr<OptionsFairring> options_;
+  DelegateFactory factory_;
+  std::mutex mu_;
+  bool have_deployment_ = false;
+  Deployment deployment_;
+  std::shared_ptr<Engine> engine_;
+  int engine_device_ = -1;
+  std::unique_ptr<CpuEngine> cpu_engine_;
+  std::map<std::string, c10::intrusive_ptr<c10d::Backend>> delegates_;
+  uint64_t seq_ = 0;
+  uint64_t delegated_ = 0;
+};
+
+}  // namespace fairring

@@ -1,0 +1,188 @@
+// Runs a whole multi-rank collective on ONE GPU: every rank's staging, flags
+// and tensors live on the same device and one cooperative launch carries the
+// blocks of all ranks (grid.y = rank).  The kernels' code is the same as in a
+// real job; only the peer pointers happen to be local.  This is how the
+// kernels are tested where fewer GPUs than ranks are available, and how a
+// timed-out wait is demonstrated without a second process: a "silent" rank's
+// signals are redirected into a scratch pad that nobody reads.
+#include <ATen/ATen.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+
+#include <tuple>
+#include <vector>
+
+#include "check.h"
+#include "engine.h"
+#include "kernels/kernels.h"
+
+namespace fairring {
+
+namespace {
+bool toDTypeEmu(at::ScalarType st, DType* out) {
+  switch (st) {
+    case at::kByte: *out = DType::U8; return true;
+    case at::kChar: *out = DType::I8; return true;
+    case at::kInt: *out = DType::I32; return true;
+    case at::kLong: *out = DType::I64; return true;
+    case at::kHalf: *out = DType::F16; return true;
+    case at::kBFloat16: *out = DType::BF16; return true;
+    case at::kFloat: *out = DType::F32; return true;
+    case at::kDouble: *out = DType::F64; return true;
+    default: return false;
+  }
+}
+}  // namespace
+
+// kind: "allreduce" | "reduce_scatter" | "allgather"
+// algo: "oneshot" | "twoshot" | "hier" (hier = the three-kernel pipeline; valid for M == 1 too)
+// Returns (outputs, status words [world][kStatusWords]).
+std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
+    const std::string& kind, std::vector<at::Tensor> inputs, int64_t gpus_per_machine,
+    bool favorable, const std::string& op, double scale, c10::optional<at::ScalarType> wire_dtype,
+    const std::string& algo, int64_t blocks, int64_t half_bytes, int64_t timeout_ms,
+    int64_t silent_rank, int64_t repeats) {
+  const int W = (int)inputs.size();
+  TORCH_CHECK(W >= 1 && W <= kMaxRanks, "1..", kMaxRanks, " emulated ranks");
+  TORCH_CHECK(gpus_per_machine >= 1 && W % gpus_per_machine == 0, "grouping must divide the world");
+  TORCH_CHECK(blocks >= 1 && blocks <= kMaxBlocks, "blocks out of range");
+  for (auto& t : inputs)
+    TORCH_CHECK(t.is_cuda() && t.device() == inputs[0].device() && t.is_contiguous() &&
+                    t.scalar_type() == inputs[0].scalar_type() && t.numel() == inputs[0].numel(),
+                "emulated ranks need same-shaped contiguous tensors on one GPU");
+  c10::cuda::CUDAGuard guard(inputs[0].device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+
+  DType io, wire;
+  TORCH_CHECK(toDTypeEmu(inputs[0].scalar_type(), &io), "unsupported dtype");
+  wire = io;
+  if (wire_dtype.has_value()) TORCH_CHECK(toDTypeEmu(*wire_dtype, &wire), "unsupported wire dtype");
+  TORCH_CHECK(comboSupported(io, wire), "unsupported (dtype, wire dtype) pair");
+  RedOp rop = op == "max" ? RedOp::MAX : (op == "min" ? RedOp::MIN : RedOp::SUM);
+  const int wes = dtypeSize(wire);
+  const int64_t V = kVecBytes / wes;
+
+  const bool is_ar = kind == "allreduce", is_rs = kind == "reduce_scatter", is_ag = kind == "allgather";
+  TORCH_CHECK(is_ar || is_rs || is_ag, "unknown collective ", kind);
+  const int64_t n_in = inputs[0].numel();
+  TORCH_CHECK(!is_rs || n_in % W == 0, "reduce_scatter input must be world * n");
+  const int64_t per_rank = is_rs ? n_in / W : n_in;
+
+  auto bopt = inputs[0].options();
+  auto u8 = bopt.dtype(at::kByte);
+  auto i32 = bopt.dtype(at::kInt);
+  std::vector<at::Tensor> staging, flags, seqs, outs;
+  for (int r = 0; r < W; ++r) {
+    staging.push_back(at::zeros({2 * half_bytes}, u8));
+    flags.push_back(at::zeros({kMaxRanks * kMaxBlocks}, i32));
+    seqs.push_back(at::zeros({kMaxBlocks}, i32));
+    if (is_ar) outs.push_back(inputs[r]);  // in place, like the real thing
+    else if (is_rs) outs.push_back(at::zeros({per_rank}, bopt));
+    else outs.push_back(at::zeros({per_rank * W}, bopt));
+  }
+  at::Tensor scratch = at::zeros({kMaxRanks * kMaxBlocks}, i32);
+  uint32_t* status_host = nullptr;
+  FR_CUDA(cudaHostAlloc((void**)&status_host, sizeof(uint32_t) * (W * kStatusWords + 1),
+                        cudaHostAllocMapped));
+  std::memset(status_host, 0, sizeof(uint32_t) * (W * kStatusWords + 1));
+  uint32_t* status_dev = nullptr;
+  FR_CUDA(cudaHostGetDevicePointer((void**)&status_dev, status_host, 0));
+
+  std::vector<ChannelDev> chs(W);
+  for (int r = 0; r < W; ++r) {
+    ChannelDev& c = chs[r];
+    std::memset(&c, 0, sizeof(c));
+    for (int p = 0; p < W; ++p) {
+      c.staging[p] = static_cast<char*>(staging[p].data_ptr());
+      c.flags[p] = static_cast<uint32_t*>(flags[p].data_ptr());
+      if (r == silent_rank && p != r) c.flags[p] = static_cast<uint32_t*>(scratch.data_ptr());
+    }
+    c.mc_staging = nullptr;
+    c.seq = static_cast<uint32_t*>(seqs[r].data_ptr());
+    c.status = status_dev + r * kStatusWords;
+    c.abort_flag = status_dev + W * kStatusWords;
+    c.half_bytes = (uint64_t)half_bytes;
+    c.timeout_ns = (uint64_t)timeout_ms * 1000000ull;
+    c.topo = makeTopo(W, (int)gpus_per_machine, favorable, r);
+  }
+  const Topo t0 = chs[0].topo;
+  at::Tensor chs_dev = at::empty({(int64_t)(sizeof(ChannelDev) * W)}, u8);
+  at::Tensor args_dev = at::empty({(int64_t)(sizeof(OpArgs) * W)}, u8);
+  FR_CUDA(cudaMemcpyAsync(chs_dev.data_ptr(), chs.data(), sizeof(ChannelDev) * W,
+                          cudaMemcpyHostToDevice, stream));
+
+  auto launchAll = [&](KernelId id, const Seg& seg, int64_t in_off, int64_t out_off, uint32_t fl) {
+    std::vector<OpArgs> as(W);
+    const int ies = dtypeSize(io);
+    for (int r = 0; r < W; ++r) {
+      OpArgs& a = as[r];
+      std::memset(&a, 0, sizeof(a));
+      a.in = static_cast<const char*>(inputs[r].data_ptr()) + in_off * ies;
+      a.out = static_cast<char*>(outs[r].data_ptr()) + out_off * ies;
+      a.seg = seg;
+      a.scale = (float)scale;
+      a.op = (int32_t)rop;
+      a.io_dtype = (int32_t)io;
+      a.wire_dtype = (int32_t)wire;
+      a.flags = fl;
+    }
+    FR_CUDA(cudaMemcpyAsync(args_dev.data_ptr(), as.data(), sizeof(OpArgs) * W,
+                            cudaMemcpyHostToDevice, stream));
+    cudaError_t e = launchEmulated(id, static_cast<const ChannelDev*>(chs_dev.data_ptr()),
+                                   static_cast<const OpArgs*>(args_dev.data_ptr()), W, (int)blocks,
+                                   stream);
+    TORCH_CHECK(e == cudaSuccess, "emulated launch of ", kernelName(id), " failed: ",
+                cudaGetErrorString(e));
+    FR_CUDA(cudaStreamSynchronize(stream));  // args_dev is reused by the next launch
+  };
+
+  for (int64_t rep = 0; rep < repeats; ++rep) {
+    if (is_ar) {
+      if (algo == "oneshot") {
+        const Seg s = allreduceSeg(n_in, wes, W);
+        TORCH_CHECK((int64_t)W * W * s.qv * kVecBytes <= half_bytes, "message too large for one-shot");
+        launchAll(KernelId::ONESHOT, s, 0, 0, kAdvanceSeq);
+      } else {
+        const SlicePlan sp = planSlices(n_in, wes, W, roundDown(half_bytes, (int64_t)kVecBytes * W));
+        for (int64_t k = 0; k < sp.num_slices; ++k) {
+          const int64_t off = k * sp.slice_elems;
+          const int64_t n = std::min(sp.slice_elems, n_in - off);
+          const Seg s = allreduceSeg(n, wes, W);
+          if (algo == "twoshot") {
+            TORCH_CHECK(t0.M == 1, "twoshot is the flat (one machine) kernel");
+            launchAll(KernelId::TWOSHOT, s, off, off, kAdvanceSeq);
+          } else {
+            launchAll(KernelId::RS_INTRAGROUP, s, off, off, 0);
+            if (t0.M > 1) launchAll(KernelId::SHARD_SERVER_REDUCE, s, off, off, 0);
+            launchAll(KernelId::AG_INTRAGROUP, s, off, off, kAdvanceSeq);
+          }
+        }
+      }
+    } else {
+      int64_t max_len = roundDown(roundDown(half_bytes, (int64_t)kVecBytes * W) / wes / W, V);
+      if (max_len < V) max_len = V;
+      for (int64_t off = 0; off < per_rank; off += max_len) {
+        const int64_t len = std::min(max_len, per_rank - off);
+        const Seg s = scatterSeg(len, per_rank, wes);
+        if (is_rs) {
+          if (t0.M == 1) {
+            launchAll(KernelId::RS_INTRAGROUP, s, off, off, kToUser | kAdvanceSeq);
+          } else {
+            launchAll(KernelId::RS_INTRAGROUP, s, off, off, 0);
+            launchAll(KernelId::SHARD_SERVER_REDUCE, s, off, off, kToUser | kAdvanceSeq);
+          }
+        } else {
+          launchAll(KernelId::DIFFUSE, s, off, off, 0);
+          launchAll(KernelId::AG_INTRAGROUP, s, off, off, kAdvanceSeq);
+        }
+      }
+    }
+  }
+  FR_CUDA(cudaStreamSynchronize(stream));
+  at::Tensor status = at::zeros({W, kStatusWords}, at::kInt);
+  std::memcpy(status.data_ptr(), status_host, sizeof(uint32_t) * W * kStatusWords);
+  cudaFreeHost(status_host);
+  return std::make_tuple(outs, status);
+}
+
+}  // namespace fairring

@@ -1,0 +1,373 @@
+#include "engine.h"
+
+#include <algorithm>
+#include <cstring>
+#include <sstream>
+
+#include "check.h"
+
+namespace fairring {
+
+const char* algoName(Algo a) {
+  switch (a) {
+    case Algo::AUTO: return "auto";
+    case Algo::ONESHOT: return "oneshot";
+    case Algo::TWOSHOT: return "twoshot";
+    case Algo::HIER: return "hier";
+    case Algo::NVLS: return "nvls";
+    case Algo::NVLS_ONESHOT: return "nvls_oneshot";
+  }
+  return "?";
+}
+
+Algo parseAlgo(const std::string& s) {
+  for (Algo a : {Algo::AUTO, Algo::ONESHOT, Algo::TWOSHOT, Algo::HIER, Algo::NVLS, Algo::NVLS_ONESHOT})
+    if (s == algoName(a)) return a;
+  FR_CHECK(false, "unknown FAIRRING_ALGO '", s,
+           "' (auto, oneshot, twoshot, hier, nvls, nvls_oneshot)");
+  return Algo::AUTO;
+}
+
+void CommandQueue::push(std::function<void()> fn) {
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    q_.push_back(std::move(fn));
+  }
+  cv_.notify_one();
+}
+
+std::function<void()> CommandQueue::pop() {
+  std::unique_lock<std::mutex> lk(mu_);
+  cv_.wait(lk, [&] { return !q_.empty(); });
+  auto fn = std::move(q_.front());
+  q_.pop_front();
+  return fn;
+}
+
+namespace {
+constexpr size_t kFlagPadBytes = (size_t)kMaxRanks * kMaxBlocks * sizeof(uint32_t);
+constexpr int kEventPool = 2048;
+}  // namespace
+
+Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
+               const EngineConfig& cfg)
+    : store_(std::move(store)), topo_(topo), device_(device), cfg_(cfg) {
+  FR_CHECK(topo_.world <= kMaxRanks, "the peer-memory path serves at most ", kMaxRanks,
+           " ranks, got ", topo_.world);
+  FR_CHECK(cfg_.blocks >= 1 && cfg_.blocks <= kMaxBlocks, "FAIRRING_BLOCKS must be in 1..",
+           kMaxBlocks);
+  FR_CUDA(cudaSetDevice(device_));
+  plan_ = planMemory(cfg_.total_memory, cfg_.slice_bytes, cfg_.parallelism, topo_.world,
+                     cfg_.min_half_bytes);
+
+  alloc_.reset(new SymmAllocator(store_, topo_.rank, topo_.world, device_, cfg_.transport,
+                                 cfg_.nvls, cfg_.bootstrap_timeout));
+  flags_bytes_ = (size_t)roundUp((int64_t)(kFlagPadBytes * plan_.channels), 64 << 10);
+  region_ = alloc_->allocate(flags_bytes_ + (size_t)plan_.slot_bytes * plan_.channels,
+                             /*want_multicast=*/true);
+
+  FR_CUDA(cudaMalloc(&seq_dev_, sizeof(uint32_t) * kMaxBlocks * plan_.channels));
+  FR_CUDA(cudaMemset(seq_dev_, 0, sizeof(uint32_t) * kMaxBlocks * plan_.channels));
+  const size_t status_words = (size_t)plan_.channels * kStatusWords + 16;
+  FR_CUDA(cudaHostAlloc((void**)&status_host_, status_words * sizeof(uint32_t),
+                        cudaHostAllocMapped));
+  std::memset(status_host_, 0, status_words * sizeof(uint32_t));
+  FR_CUDA(cudaHostGetDevicePointer((void**)&status_dev_, status_host_, 0));
+
+  int lo = 0, hi = 0;
+  FR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+  channels_.resize(plan_.channels);
+  for (int c = 0; c < plan_.channels; ++c) {
+    Channel& ch = channels_[c];
+    FR_CUDA(cudaStreamCreateWithPriority(&ch.stream, cudaStreamNonBlocking,
+                                         cfg_.high_priority ? hi : lo));
+    FR_CUDA(cudaEventCreateWithFlags(&ch.done, cudaEventDisableTiming));
+    for (int r = 0; r < topo_.world; ++r) {
+      char* base = static_cast<char*>(region_.ptrs[r]);
+      ch.dev.flags[r] = reinterpret_cast<uint32_t*>(base + kFlagPadBytes * c);
+      ch.dev.staging[r] = base + flags_bytes_ + (size_t)plan_.slot_bytes * c;
+    }
+    ch.dev.mc_staging = region_.mc_ptr
+                            ? static_cast<char*>(region_.mc_ptr) + flags_bytes_ +
+                                  (size_t)plan_.slot_bytes * c
+                            : nullptr;
+    ch.dev.seq = seq_dev_ + (size_t)kMaxBlocks * c;
+    ch.dev.status = status_dev_ + (size_t)kStatusWords * c;
+    ch.dev.abort_flag = status_dev_ + (size_t)kStatusWords * plan_.channels;
+    ch.dev.half_bytes = (uint64_t)plan_.half_bytes;
+    ch.dev.timeout_ns = cfg_.device_timeout_ns;
+    ch.dev.topo = topo_;
+  }
+  events_.resize(kEventPool);
+  for (auto& e : events_) FR_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  FR_CUDA(cudaDeviceSynchronize());
+  store_->barrier("engine/ready", topo_.world, cfg_.bootstrap_timeout);
+
+  if (cfg_.command_thread) {
+    worker_ = std::thread([this] {
+      cudaSetDevice(device_);
+      for (;;) {
+        auto fn = queue_.pop();
+        if (!fn) break;
+        fn();
+      }
+    });
+  }
+}
+
+Engine::~Engine() {
+  if (worker_.joinable()) {
+    queue_.push(std::function<void()>());
+    worker_.join();
+  }
+  cudaSetDevice(device_);
+  cudaDeviceSynchronize();
+  try {
+    alloc_->release(region_);
+  } catch (const std::exception&) {
+  }
+  for (auto& ch : channels_) {
+    if (ch.stream) cudaStreamDestroy(ch.stream);
+    if (ch.done) cudaEventDestroy(ch.done);
+  }
+  for (auto& e : events_)
+    if (e) cudaEventDestroy(e);
+  if (seq_dev_) cudaFree(seq_dev_);
+  if (status_host_) cudaFreeHost(status_host_);
+}
+
+cudaEvent_t Engine::nextEvent() {
+  cudaEvent_t e = events_[next_event_];
+  next_event_ = (next_event_ + 1) % events_.size();
+  return e;
+}
+
+cudaEvent_t Engine::begin(cudaStream_t caller) {
+  std::lock_guard<std::mutex> lk(mu_);
+  cudaEvent_t e = nextEvent();
+  FR_CUDA(cudaEventRecord(e, caller));
+  return e;
+}
+
+void Engine::submit(std::function<void()> fn) {
+  if (cfg_.command_thread)
+    queue_.push(std::move(fn));
+  else
+    fn();
+}
+
+uint32_t Engine::health(std::string* what) const {
+  for (int c = 0; c < plan_.channels; ++c) {
+    const volatile uint32_t* s = status_host_ + (size_t)kStatusWords * c;
+    if (s[0] != kStatusOk) {
+      if (what) {
+        std::ostringstream os;
+        os << "channel " << c << ": " << (s[0] == kStatusTimeout ? "timed out" : "aborted")
+           << " waiting for rank " << s[2] << " at barrier " << s[1] << " of collective " << s[3];
+        *what = os.str();
+      }
+      return s[0];
+    }
+  }
+  return kStatusOk;
+}
+
+void Engine::checkHealth() {
+  std::string what;
+  if (poisoned_ || health(&what) != kStatusOk) {
+    poisoned_ = true;
+    if (what.empty()) what = "an earlier collective failed";
+    FR_CHECK(false, "the fairring engine is in a failed state (", what,
+             "); call reset() on every rank to recover");
+  }
+}
+
+void Engine::abort() {
+  status_host_[(size_t)kStatusWords * plan_.channels] = 1;
+  poisoned_ = true;
+}
+
+void Engine::reset() {
+  std::lock_guard<std::mutex> lk(mu_);
+  FR_CUDA(cudaSetDevice(device_));
+  FR_CUDA(cudaDeviceSynchronize());
+  const std::string pfx = "engine/reset" + std::to_string(reset_count_++);
+  store_->barrier(pfx + "/quiet", topo_.world, cfg_.bootstrap_timeout);
+  FR_CUDA(cudaMemset(region_.ptrs[topo_.rank], 0, flags_bytes_));
+  FR_CUDA(cudaMemset(seq_dev_, 0, sizeof(uint32_t) * kMaxBlocks * plan_.channels));
+  FR_CUDA(cudaDeviceSynchronize());
+  std::memset(status_host_, 0, ((size_t)plan_.channels * kStatusWords + 16) * sizeof(uint32_t));
+  poisoned_ = false;
+  store_->barrier(pfx + "/clean", topo_.world, cfg_.bootstrap_timeout);
+}
+
+EngineStats Engine::stats() const { return stats_; }
+
+std::vector<cudaStream_t> Engine::streams() const {
+  std::vector<cudaStream_t> v;
+  for (auto& ch : channels_) v.push_back(ch.stream);
+  return v;
+}
+
+std::string Engine::describe() const {
+  std::ostringstream os;
+  os << "world=" << topo_.world << " grouping=" << topo_.M << "x" << topo_.D
+     << (topo_.favorable ? " (device-major ranks)" : " (machine-major ranks)")
+     << " transport=" << alloc_->describe() << " nvls=" << (nvlsAvailable() ? "yes" : "no")
+     << " channels=" << plan_.channels << " half_slot=" << plan_.half_bytes
+     << "B max_slice=" << plan_.max_slice_bytes << "B blocks=" << cfg_.blocks
+     << " algo=" << algoName(cfg_.algo);
+  return os.str();
+}
+
+Algo Engine::chooseAllreduce(int64_t wire_bytes, DType wire, RedOp op) const {
+  const int W = topo_.world;
+  const int64_t qv = std::max<int64_t>(1, ceilDiv(ceilDiv(wire_bytes, kVecBytes), W));
+  const bool oneshot_fits = (int64_t)W * W * qv * kVecBytes <= plan_.half_bytes;
+  const bool nvls_ok = nvlsAvailable() && nvlsSupported(wire, op);
+  Algo a = cfg_.algo;
+  if (a == Algo::ONESHOT && !oneshot_fits) a = Algo::AUTO;
+  if ((a == Algo::NVLS || a == Algo::NVLS_ONESHOT) && !nvls_ok) a = Algo::AUTO;
+  if (a == Algo::TWOSHOT && topo_.M > 1) a = Algo::HIER;
+  if (a != Algo::AUTO) return a;
+  if (wire_bytes <= cfg_.oneshot_max_bytes && oneshot_fits) return Algo::ONESHOT;
+  if (topo_.M > 1) return Algo::HIER;
+  if (nvls_ok) {
+    if (wire_bytes <= cfg_.nvls_oneshot_max_bytes) return Algo::NVLS_ONESHOT;
+    if (wire_bytes >= cfg_.nvls_min_bytes) return Algo::NVLS;
+  }
+  return Algo::TWOSHOT;
+}
+
+void Engine::launch(Channel& ch, KernelId id, const OpArgs& a) {
+  cudaError_t e = launchCollective(id, ch.dev, a, cfg_.blocks, ch.stream);
+  FR_CHECK(e == cudaSuccess, "launch of ", kernelName(id), " failed: ", cudaGetErrorString(e));
+  ++stats_.launches[(size_t)id];
+}
+
+void Engine::runAllreduceSlice(Channel& ch, const CollectiveDesc& d, const void* in, void* out,
+                               int64_t n, Algo algo) {
+  OpArgs a{};
+  a.in = in;
+  a.out = out;
+  a.seg = allreduceSeg(n, dtypeSize(d.wire), topo_.world);
+  a.scale = d.scale;
+  a.op = (int32_t)d.op;
+  a.io_dtype = (int32_t)d.io;
+  a.wire_dtype = (int32_t)d.wire;
+  switch (algo) {
+    case Algo::ONESHOT:
+      a.flags = kAdvanceSeq;
+      launch(ch, KernelId::ONESHOT, a);
+      break;
+    case Algo::TWOSHOT:
+      a.flags = kAdvanceSeq;
+      launch(ch, KernelId::TWOSHOT, a);
+      break;
+    case Algo::NVLS:
+      a.flags = kAdvanceSeq;
+      launch(ch, KernelId::NVLS_TWOSHOT, a);
+      break;
+    case Algo::NVLS_ONESHOT:
+      a.flags = kAdvanceSeq;
+      launch(ch, KernelId::NVLS_ONESHOT, a);
+      break;
+    case Algo::HIER:
+    default:
+      a.flags = 0;
+      launch(ch, KernelId::RS_INTRAGROUP, a);
+      if (topo_.M > 1) launch(ch, KernelId::SHARD_SERVER_REDUCE, a);
+      a.flags = kAdvanceSeq;
+      launch(ch, KernelId::AG_INTRAGROUP, a);
+      break;
+  }
+}
+
+cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after) {
+  std::lock_guard<std::mutex> lk(mu_);
+  checkHealth();
+  FR_CHECK(comboSupported(d.io, d.wire), "no kernel for this (tensor dtype, wire dtype) pair");
+  const int W = topo_.world;
+  const int ies = dtypeSize(d.io), wes = dtypeSize(d.wire);
+  const int64_t V = kVecBytes / wes;
+  std::vector<int> used;
+  auto take = [&]() -> Channel& {
+    const int c = (int)(next_channel_++ % channels_.size());
+    if (std::find(used.begin(), used.end(), c) == used.end()) {
+      FR_CUDA(cudaStreamWaitEvent(channels_[c].stream, after, 0));
+      used.push_back(c);
+    }
+    return channels_[c];
+  };
+  const char* in = static_cast<const char*>(d.in);
+  char* out = static_cast<char*>(d.out);
+  ++stats_.collectives;
+
+  if (d.kind == CollKind::ALLREDUCE) {
+    const int64_t bytes = d.numel * wes;
+    const Algo whole = chooseAllreduce(bytes, d.wire, d.op);
+    if (whole == Algo::ONESHOT ||
+        (whole == Algo::NVLS_ONESHOT && bytes <= plan_.max_slice_bytes)) {
+      runAllreduceSlice(take(), d, in, out, d.numel, whole);
+      ++stats_.slices;
+    } else {
+      const SlicePlan sp = planSlices(d.numel, wes, W, plan_.max_slice_bytes);
+      for (int64_t k = 0; k < sp.num_slices; ++k) {
+        const int64_t off = k * sp.slice_elems;
+        const int64_t n = std::min(sp.slice_elems, d.numel - off);
+        Algo a = chooseAllreduce(n * wes, d.wire, d.op);
+        if (a == Algo::ONESHOT && sp.num_slices > 1) a = topo_.M > 1 ? Algo::HIER : Algo::TWOSHOT;
+        runAllreduceSlice(take(), d, in + off * ies, out + off * ies, n, a);
+        ++stats_.slices;
+      }
+    }
+    stats_.wire_bytes += (uint64_t)bytes;
+  } else {
+    int64_t max_len = roundDown(plan_.max_slice_bytes / wes / W, V);
+    if (max_len < V) max_len = V;
+    for (int64_t off = 0; off < d.numel; off += max_len) {
+      const int64_t len = std::min(max_len, d.numel - off);
+      OpArgs a{};
+      a.in = in + off * ies;
+      a.out = out + off * ies;
+      a.seg = scatterSeg(len, d.numel, wes);
+      a.scale = d.scale;
+      a.op = (int32_t)d.op;
+      a.io_dtype = (int32_t)d.io;
+      a.wire_dtype = (int32_t)d.wire;
+      Channel& ch = take();
+      if (d.kind == CollKind::REDUCE_SCATTER) {
+        if (topo_.M == 1) {
+          a.flags = kToUser | kAdvanceSeq;
+          launch(ch, KernelId::RS_INTRAGROUP, a);
+        } else {
+          a.flags = 0;
+          launch(ch, KernelId::RS_INTRAGROUP, a);
+          a.flags = kToUser | kAdvanceSeq;
+          launch(ch, KernelId::SHARD_SERVER_REDUCE, a);
+        }
+      } else {
+        a.flags = 0;
+        launch(ch, KernelId::DIFFUSE, a);
+        a.flags = kAdvanceSeq;
+        launch(ch, KernelId::AG_INTRAGROUP, a);
+      }
+      ++stats_.slices;
+    }
+    stats_.wire_bytes += (uint64_t)d.numel * wes * W;
+  }
+
+  if (used.empty()) {  // zero elements: still give the caller a stream ordered after `after`
+    Channel& ch = take();
+    return ch.stream;
+  }
+  Channel& join = channels_[used[0]];
+  for (size_t i = 1; i < used.size(); ++i) {
+    Channel& ch = channels_[used[i]];
+    FR_CUDA(cudaEventRecord(ch.done, ch.stream));
+    FR_CUDA(cudaStreamWaitEvent(join.stream, ch.done, 0));
+  }
+  return join.stream;
+}
+
+}  // namespace fairring

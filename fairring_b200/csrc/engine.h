@@ -1,0 +1,155 @@
+// Per-GPU engine: owns the symmetric staging memory, the channels (slot + flag
+// pad + side stream each), picks a kernel variant per slice and enqueues the
+// kernels.  Counterpart of DeviceFairring in the reference
+// (fairring/device.{h,cc}): there, five stage streams run NCCL calls chained by
+// events and a command thread does the enqueueing; here a slice is one to three
+// kernel launches on one of `channels` side streams, consecutive slices go to
+// different channels so they overlap, and the command thread is optional
+// because a kernel launch never blocks.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <array>
+#include <atomic>
+#include <chrono>
+#include <condition_variable>
+#include <deque>
+#include <functional>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "kernels/kernels.h"
+#include "kvstore.h"
+#include "layout.h"
+#include "symmem.h"
+
+namespace fairring {
+
+enum class Algo : int32_t { AUTO = 0, ONESHOT, TWOSHOT, HIER, NVLS, NVLS_ONESHOT };
+const char* algoName(Algo a);
+Algo parseAlgo(const std::string& s);
+
+struct EngineConfig {
+  int64_t total_memory = 50ll << 20;   // FAIRRING_TOTAL_MEMORY
+  int64_t slice_bytes = 25ll << 20;    // FAIRRING_SLICE_SIZE
+  int32_t parallelism = 16;            // FAIRRING_PARALLELISM: slices in flight
+  int64_t min_half_bytes = 4ll << 20;  // channels are merged until a half-slot is at least this
+  int32_t blocks = 32;                 // thread blocks per kernel (SM budget)
+  int64_t oneshot_max_bytes = 256 << 10;
+  int64_t nvls_min_bytes = 0;          // below this the peer-load two-shot is used
+  int64_t nvls_oneshot_max_bytes = 2 << 20;
+  uint64_t device_timeout_ns = 30ull * 1000 * 1000 * 1000;
+  Algo algo = Algo::AUTO;
+  bool high_priority = true;
+  bool command_thread = false;
+  SymmTransport transport = SymmTransport::AUTO;
+  NvlsMode nvls = NvlsMode::AUTO;
+  std::chrono::milliseconds bootstrap_timeout{120000};
+};
+
+enum class CollKind : int32_t { ALLREDUCE = 0, REDUCE_SCATTER, ALLGATHER };
+
+struct CollectiveDesc {
+  CollKind kind = CollKind::ALLREDUCE;
+  const void* in = nullptr;
+  void* out = nullptr;
+  int64_t numel = 0;   // all_reduce: total elements; the others: elements per rank
+  DType io = DType::F32;
+  DType wire = DType::F32;
+  RedOp op = RedOp::SUM;
+  float scale = 1.0f;
+};
+
+struct EngineStats {
+  uint64_t collectives = 0;
+  uint64_t slices = 0;
+  uint64_t wire_bytes = 0;
+  std::array<uint64_t, (size_t)KernelId::kCount> launches{};
+};
+
+// FIFO of closures drained by one thread (fairring/utils.h:329-351 in the
+// reference).  Used when FAIRRING_COMMAND_THREAD=1.
+class CommandQueue {
+ public:
+  void push(std::function<void()> fn);
+  // Blocks; an empty function means "stop".
+  std::function<void()> pop();
+ private:
+  std::mutex mu_;
+  std::condition_variable cv_;
+  std::deque<std::function<void()>> q_;
+};
+
+class Engine {
+ public:
+  // Collective over the group.  `device` must be the current CUDA device.
+  Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device, const EngineConfig& cfg);
+  ~Engine();
+
+  // Record "the caller's work so far" so that a later run() can order itself
+  // after it; cheap, called on the caller's thread.
+  cudaEvent_t begin(cudaStream_t caller);
+  // Enqueue the whole collective.  Returns the side stream on which everything
+  // it launched is ordered; the caller records its completion event there.
+  cudaStream_t run(const CollectiveDesc& d, cudaEvent_t after);
+  // Run `fn` now, or on the command thread when one is configured.
+  void submit(std::function<void()> fn);
+
+  // Throws if a kernel reported a timeout/abort since the last call.
+  void checkHealth();
+  // Non-throwing variant: code (StatusCode) and a description.
+  uint32_t health(std::string* what) const;
+  // Makes every device-side wait give up (host-visible flag).
+  void abort();
+  // Collective: after a failure, bring flags and sequence numbers back to zero.
+  void reset();
+
+  const Topo& topo() const { return topo_; }
+  const MemoryPlan& plan() const { return plan_; }
+  const EngineConfig& config() const { return cfg_; }
+  EngineStats stats() const;
+  bool nvlsAvailable() const { return region_.mc_ptr != nullptr; }
+  std::string describe() const;
+  Algo chooseAllreduce(int64_t wire_bytes, DType wire, RedOp op) const;
+  std::vector<cudaStream_t> streams() const;
+
+ private:
+  struct Channel {
+    cudaStream_t stream = nullptr;
+    ChannelDev dev{};
+    cudaEvent_t done = nullptr;
+  };
+  void launch(Channel& ch, KernelId id, const OpArgs& a);
+  void runAllreduceSlice(Channel& ch, const CollectiveDesc& d, const void* in, void* out,
+                         int64_t n, Algo algo);
+  cudaEvent_t nextEvent();
+
+  std::shared_ptr<KvStore> store_;
+  Topo topo_;
+  int device_;
+  EngineConfig cfg_;
+  MemoryPlan plan_;
+  std::unique_ptr<SymmAllocator> alloc_;
+  SymmRegion region_;
+  size_t flags_bytes_ = 0;
+  uint32_t* seq_dev_ = nullptr;
+  uint32_t* status_host_ = nullptr;  // pinned + mapped: [channels][kStatusWords], then abort word
+  uint32_t* status_dev_ = nullptr;
+  std::vector<Channel> channels_;
+  std::vector<cudaEvent_t> events_;
+  size_t next_event_ = 0;
+  uint64_t next_channel_ = 0;
+  std::mutex mu_;
+  EngineStats stats_;
+  bool poisoned_ = false;
+  int reset_count_ = 0;
+
+  CommandQueue queue_;
+  std::thread worker_;
+};
+
+}  // namespace fairring

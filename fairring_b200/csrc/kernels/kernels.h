@@ -1,0 +1,87 @@
+// Host-visible interface of the sm_100a collective kernels.  Nothing here
+// depends on torch; the engine fills these PODs and calls launch*().
+//
+// The kernels replace the library calls the reference strings together per
+// slice (fairring/device.cc:444-634: ncclReduceScatter, ncclSend/ncclRecv,
+// at::sum_out, ncclSend/ncclRecv, ncclAllGather) with loads and stores on peer
+// GPUs' staging memory issued from inside the kernel.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../layout.h"
+
+namespace fairring {
+
+// Everything one channel's kernels need to reach their peers.  Passed by
+// value (it is ~230 bytes).  A channel owns one staging slot (two halves used
+// alternately by consecutive collectives), one flag pad and one stream.
+struct ChannelDev {
+  char* staging[kMaxRanks];     // rank p's slot as mapped in this process
+  uint32_t* flags[kMaxRanks];   // rank p's flag pad: [source rank][block]
+  char* mc_staging;             // NVLS multicast alias of the slot, or null
+  uint32_t* seq;                // local, [kMaxBlocks]: collectives done by block b
+  uint32_t* status;             // host-mapped, kStatusWords words, 0 == healthy
+  const uint32_t* abort_flag;   // host-mapped; non-zero makes every wait give up
+  uint64_t half_bytes;
+  uint64_t timeout_ns;          // limit of one wait on a peer
+  Topo topo;
+};
+
+constexpr int kStatusWords = 4;  // code, barrier index, peer, sequence number
+enum StatusCode : uint32_t { kStatusOk = 0, kStatusTimeout = 1, kStatusAborted = 2 };
+
+enum OpFlags : uint32_t {
+  kToUser = 1u << 0,      // reduced data goes to `out`, not to staging (reduce_scatter)
+  kAdvanceSeq = 1u << 1,  // last kernel of the collective: bump the sequence number
+};
+
+struct OpArgs {
+  const void* in;   // slice base in the user's input
+  void* out;        // slice base in the user's output (may alias `in`)
+  Seg seg;
+  float scale;      // multiplied in while the data is first read (floating types)
+  int32_t op;       // RedOp
+  int32_t io_dtype;    // DType of in/out
+  int32_t wire_dtype;  // DType held in staging and sent over NVLink
+  uint32_t flags;      // OpFlags
+};
+
+enum class KernelId : int32_t {
+  ONESHOT = 0,          // push everything to everyone, one barrier, local reduce
+  TWOSHOT,              // rs_intragroup + ag_intragroup in one launch (M == 1)
+  RS_INTRAGROUP,        // push to group peers, reduce own rail chunks into the self slot
+  SHARD_SERVER_REDUCE,  // pull own shard from rail peers, reduce, push it back to them
+  AG_INTRAGROUP,        // pull reduced rail chunks from group peers into the user tensor
+  DIFFUSE,              // all_gather stage 1: own chunk -> self slot of every rail peer
+  NVLS_TWOSHOT,         // multimem.ld_reduce own chunk, multimem.st it to all
+  NVLS_ONESHOT,         // multimem.ld_reduce the whole message
+  kCount
+};
+
+const char* kernelName(KernelId id);
+
+// Which (io, wire) pairs have kernels: io == wire for all eight dtypes, plus
+// fp32 tensors carried as bf16 or fp16 on the wire.
+bool comboSupported(DType io, DType wire);
+// multimem.ld_reduce exists only for some (dtype, op) pairs.
+bool nvlsSupported(DType wire, RedOp op);
+
+constexpr int kThreads = 512;
+
+// One rank per process: the usual launch.
+cudaError_t launchCollective(KernelId id, const ChannelDev& ch, const OpArgs& args,
+                             int blocks, cudaStream_t stream);
+
+// All `world` ranks inside one cooperative launch on one GPU (grid.y = rank):
+// how the multi-rank logic is exercised when fewer GPUs than ranks are at hand.
+// `chs` and `args` are device arrays of `world` entries.
+cudaError_t launchEmulated(KernelId id, const ChannelDev* chs, const OpArgs* args,
+                           int world, int blocks, cudaStream_t stream);
+
+// Number of kernels this library has launched in this process.
+uint64_t launchCount();
+
+}  // namespace fairring

@@ -1,0 +1,71 @@
+#include "local_ops.h"
+
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/extension.h>
+
+#include <cmath>
+
+#include "kernels/local_kernels.h"
+
+namespace fairring {
+
+namespace {
+void checkFlat(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous(), name,
+              " must be a contiguous fp32 CUDA tensor");
+}
+
+// One AdamW step over flat buffers, in place.  `step` counts from 1.
+void adamwFlat(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, double lr, double beta1,
+               double beta2, double eps, double weight_decay, int64_t step, double grad_scale) {
+  checkFlat(p, "param");
+  checkFlat(g, "grad");
+  checkFlat(m, "exp_avg");
+  checkFlat(v, "exp_avg_sq");
+  TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(),
+              "flat buffers must have the same length");
+  TORCH_CHECK(step >= 1, "step counts from 1");
+  c10::cuda::CUDAGuard guard(p.device());
+  AdamWArgs a;
+  a.lr = (float)lr;
+  a.beta1 = (float)beta1;
+  a.beta2 = (float)beta2;
+  a.eps = (float)eps;
+  a.weight_decay = (float)weight_decay;
+  a.step_size = (float)(lr / (1.0 - std::pow(beta1, (double)step)));
+  a.inv_sqrt_bias2 = (float)(1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step)));
+  a.grad_scale = (float)grad_scale;
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  cudaError_t e = launchAdamWFlat(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(),
+                                  v.data_ptr<float>(), p.numel(), a, sms,
+                                  c10::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "adamw_flat launch failed: ", cudaGetErrorString(e));
+}
+
+// Sum of squares of a flat fp32 buffer, as a 1-element device tensor.
+at::Tensor sumSq(at::Tensor x) {
+  checkFlat(x, "input");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor out = at::zeros({1}, x.options());
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  cudaError_t e = launchSumSq(x.data_ptr<float>(), x.numel(), out.data_ptr<float>(), sms,
+                              c10::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "sumsq launch failed: ", cudaGetErrorString(e));
+  return out;
+}
+}  // namespace
+
+uint64_t localLaunchCount() { return localLaunchCountImpl(); }
+
+void bindLocalOps(pybind11::module_& m) {
+  namespace py = pybind11;
+  m.def("adamw_flat_", &adamwFlat, py::arg("param"), py::arg("grad"), py::arg("exp_avg"),
+        py::arg("exp_avg_sq"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"),
+        py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale") = 1.0);
+  m.def("sumsq", &sumSq, py::arg("x"));
+}
+
+}  // namespace fairring
