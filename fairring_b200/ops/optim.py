@@ -1,0 +1,55 @@
+"""Optimizers that run as one fused kernel over flat buffers."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _C
+
+
+class FlatAdamW:
+    """AdamW (decoupled weight decay, same update as ``torch.optim.AdamW``) over
+    one flat fp32 parameter buffer and one flat fp32 gradient buffer: a single
+    kernel launch per step for the whole model.
+
+    Use with :class:`fairring_b200.parallel.FlatDataParallel`::
+
+        ddp = FlatDataParallel(model)
+        opt = FlatAdamW(ddp.flat_param, ddp.flat_grad, lr=1e-4)
+    """
+
+    def __init__(self, flat_param: torch.Tensor, flat_grad: torch.Tensor, lr: float = 1e-3,
+                 betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.01):
+        if flat_param.shape != flat_grad.shape or flat_param.dim() != 1:
+            raise ValueError("flat_param and flat_grad must be 1-D and equally long")
+        self.param = flat_param
+        self.grad = flat_grad
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.exp_avg = torch.zeros_like(flat_param)
+        self.exp_avg_sq = torch.zeros_like(flat_param)
+        self.step_count = 0
+
+    def grad_norm(self) -> torch.Tensor:
+        """Global L2 norm of the gradient (1-element device tensor)."""
+        return _C.sumsq(self.grad).sqrt()
+
+    @torch.no_grad()
+    def step(self, grad_scale: float = 1.0) -> None:
+        self.step_count += 1
+        _C.adamw_flat_(self.param, self.grad, self.exp_avg, self.exp_avg_sq, self.lr,
+                       self.betas[0], self.betas[1], self.eps, self.weight_decay,
+                       self.step_count, grad_scale)
+
+    def zero_grad(self, set_to_none: bool = True) -> None:  # noqa: ARG002
+        """Gradients are overwritten by the next backward; nothing to do."""
+
+    def state_dict(self) -> dict:
+        return {"step": self.step_count, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,
+                "lr": self.lr, "betas": self.betas, "eps": self.eps,
+                "weight_decay": self.weight_decay}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.step_count = int(sd["step"])
+        self.exp_avg.copy_(sd["exp_avg"])
+        self.exp_avg_sq.copy_(sd["exp_avg_sq"])

@@ -1,0 +1,199 @@
+"""Data-parallel training on top of the fairring backend.
+
+Two ways to use the backend for gradient all-reduce:
+
+* ``torch.nn.parallel.DistributedDataParallel`` unchanged (the backend is a
+  drop-in c10d backend), optionally with :func:`fused_allreduce_hook` so that
+  the 1/W scale and a bf16/fp16 wire cast happen inside the all-reduce kernels
+  instead of in separate passes over the bucket;
+
+* :class:`FlatDataParallel`, which owns ONE flat fp32 parameter buffer and ONE
+  flat gradient buffer laid out in backward order.  Gradient buckets are
+  contiguous ranges of the flat gradient buffer, so a bucket is all-reduced in
+  place the moment its last gradient lands -- no bucket copy-in/copy-out -- on
+  the backend's side streams while backward continues, and the optimizer step
+  is a single fused kernel over the flat buffers
+  (:class:`fairring_b200.ops.FlatAdamW`).
+
+The reference has no training code; what it serves is DDP's bucketed gradient
+all-reduce overlapped with backward (README.md:104-110).
+"""
+
+from __future__ import annotations
+
+from typing import Iterable
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import get_backend
+
+
+class FusedHookState:
+    """State for :func:`fused_allreduce_hook`."""
+
+    def __init__(self, process_group=None, wire_dtype: torch.dtype | None = None):
+        self.process_group = process_group if process_group is not None else dist.group.WORLD
+        self.backend = get_backend(self.process_group, "cuda")
+        self.world = dist.get_world_size(self.process_group)
+        self.wire_dtype = wire_dtype
+
+
+def fused_allreduce_hook(state: FusedHookState, bucket: dist.GradBucket) -> torch.futures.Future:
+    """DDP communication hook: average the bucket with scale and cast fused.
+
+    DDP does not pre-divide gradients when a hook is registered, so the kernels
+    read the raw sums, multiply by 1/W while pushing, and (optionally) carry
+    them as bf16/fp16 over NVLink.
+    """
+    buf = bucket.buffer()
+    work = state.backend.allreduce_fused(buf, 1.0 / state.world, state.wire_dtype, "sum")
+    return work.get_future().then(lambda f: f.value()[0])
+
+
+class FlatDataParallel(nn.Module):
+    """Flat-buffer data parallelism (see module docstring).
+
+    ``bucket_cap_mb`` matches DDP's default of 25 MiB, the size the reference
+    tunes its slices for (README.md:62).
+    """
+
+    def __init__(self, module: nn.Module, process_group=None, bucket_cap_mb: float = 25.0,
+                 wire_dtype: torch.dtype | None = None, broadcast_parameters: bool = True):
+        super().__init__()
+        self.module = module
+        self.process_group = process_group if process_group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.process_group)
+        self.wire_dtype = wire_dtype
+        params = [p for p in module.parameters() if p.requires_grad]
+        if not params:
+            raise ValueError("module has no trainable parameters")
+        dev = params[0].device
+        if dev.type != "cuda":
+            raise ValueError("FlatDataParallel needs the module on a CUDA device")
+        for p in params:
+            if p.dtype != torch.float32 or p.device != dev:
+                raise ValueError("FlatDataParallel expects fp32 parameters on one device")
+        self.device = dev
+        self.backend = get_backend(self.process_group, "cuda")
+
+        # Backward produces gradients roughly in reverse registration order, so
+        # lay the buffers out in that order: bucket 0 fills first.
+        order = list(reversed(params))
+        align = 64  # elements: keeps every parameter 256-byte aligned
+        offsets, total = [], 0
+        for p in order:
+            offsets.append(total)
+            total += (p.numel() + align - 1) // align * align
+        self.flat_param = torch.zeros(total, device=dev, dtype=torch.float32)
+        self.flat_grad = torch.zeros(total, device=dev, dtype=torch.float32)
+        self._params = order
+        self._offsets = offsets
+        for p, off in zip(order, offsets):
+            view = self.flat_param[off:off + p.numel()].view_as(p)
+            view.copy_(p.data)
+            p.data = view
+            p.grad = None
+
+        cap = int(bucket_cap_mb * 1024 * 1024) // 4
+        self._bucket_of: dict[int, int] = {}
+        self._buckets: list[tuple[int, int]] = []  # [start, end) in elements
+        self._bucket_size: list[int] = []
+        start, count = 0, 0
+        for i, (p, off) in enumerate(zip(order, offsets)):
+            end = offsets[i + 1] if i + 1 < len(order) else total
+            self._bucket_of[id(p)] = len(self._buckets)
+            count += 1
+            if end - start >= cap or i + 1 == len(order):
+                self._buckets.append((start, end))
+                self._bucket_size.append(count)
+                start, count = end, 0
+        self._pending = list(self._bucket_size)
+        self._next_to_launch = 0
+        self._works: list = []
+        self._callback_queued = False
+        self._accumulate = False
+        self.require_backward_grad_sync = True
+        self._off_of = {id(p): off for p, off in zip(order, offsets)}
+        for p in order:
+            p.register_post_accumulate_grad_hook(self._on_grad)
+
+        if broadcast_parameters and self.world > 1:
+            dist.broadcast(self.flat_param, src=dist.get_global_rank(self.process_group, 0)
+                           if self.process_group is not dist.group.WORLD else 0,
+                           group=self.process_group)
+
+    # -- public ------------------------------------------------------------
+    @property
+    def num_buckets(self) -> int:
+        return len(self._buckets)
+
+    def forward(self, *args, **kwargs):
+        return self.module(*args, **kwargs)
+
+    def zero_grad(self, set_to_none: bool = True) -> None:  # noqa: ARG002
+        """Nothing to clear: every backward overwrites the flat gradient buffer."""
+        self._accumulate = False
+
+    def no_sync(self):
+        """Context manager: accumulate locally, skip the all-reduce (like DDP's)."""
+        outer = self
+
+        class _NoSync:
+            def __enter__(self_inner):
+                outer.require_backward_grad_sync = False
+
+            def __exit__(self_inner, *exc):
+                outer.require_backward_grad_sync = True
+                outer._accumulate = True
+
+        return _NoSync()
+
+    # -- backward machinery ---------------------------------------------------
+    def _on_grad(self, p: torch.Tensor) -> None:
+        off = self._off_of[id(p)]
+        dst = self.flat_grad[off:off + p.numel()].view_as(p)
+        if self._accumulate:
+            dst.add_(p.grad)
+        else:
+            dst.copy_(p.grad)
+        p.grad = None  # the flat buffer is the gradient; views are handed out by grads()
+        if not self._callback_queued:
+            torch.autograd.Variable._execution_engine.queue_callback(self._finish_backward)
+            self._callback_queued = True
+        b = self._bucket_of[id(p)]
+        self._pending[b] -= 1
+        if self.require_backward_grad_sync:
+            # Launch strictly in bucket order so that every rank issues the
+            # same sequence of collectives.
+            while self._next_to_launch < len(self._buckets) and self._pending[self._next_to_launch] <= 0:
+                self._launch(self._next_to_launch)
+                self._next_to_launch += 1
+
+    def _launch(self, b: int) -> None:
+        if self.world == 1:
+            return
+        s, e = self._buckets[b]
+        self._works.append(
+            self.backend.allreduce_fused(self.flat_grad[s:e], 1.0 / self.world, self.wire_dtype, "sum")
+        )
+
+    def _finish_backward(self) -> None:
+        if self.require_backward_grad_sync:
+            while self._next_to_launch < len(self._buckets):  # parameters that got no gradient
+                self._launch(self._next_to_launch)
+                self._next_to_launch += 1
+            for w in self._works:
+                w.wait()  # stream-level: the compute stream waits, the host does not
+            self._accumulate = False
+        else:
+            self._accumulate = True
+        self._works = []
+        self._pending = list(self._bucket_size)
+        self._next_to_launch = 0
+        self._callback_queued = False
+
+    def grads(self) -> Iterable[torch.Tensor]:
+        for p, off in zip(self._params, self._offsets):
+            yield self.flat_grad[off:off + p.numel()].view_as(p)

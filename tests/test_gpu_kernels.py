@@ -1,0 +1,231 @@
+"""The collective kernels against a plain PyTorch reference, on ONE GPU.
+
+All ranks of a collective are emulated inside one cooperative launch (grid.y =
+rank): the device code is exactly what runs in a multi-GPU job, only the peer
+pointers are local.  Covers every kernel except the NVLS ones (which need one
+GPU per rank), all dtypes, ragged tails, misaligned tensors, every grouping
+and both rank numberings, the double-buffered staging (repeats) and a wait
+that runs into its time limit.
+"""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.uint8, torch.int8, torch.int32, torch.int64, torch.float16, torch.bfloat16,
+          torch.float32, torch.float64]
+
+
+def _need_gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+
+
+def _make(world, n, dtype, seed=0, offset=0):
+    outs = []
+    for r in range(world):
+        g = torch.Generator(device="cpu").manual_seed(seed * 100 + r)
+        if dtype.is_floating_point:
+            t = torch.randn(n + offset, generator=g)
+        else:
+            t = torch.randint(0, 12, (n + offset,), generator=g)
+        t = t.to(dtype).cuda()
+        outs.append(t[offset:] if offset else t)
+    return outs
+
+
+def _ref(inputs, op):
+    st = torch.stack([t.double() for t in inputs])
+    return {"sum": st.sum(0), "max": st.max(0).values, "min": st.min(0).values}[op]
+
+
+def _tol(dtype, world):
+    if dtype in (torch.float16, torch.bfloat16):
+        return dict(rtol=2e-2, atol=2e-2 * world)
+    if dtype == torch.float32:
+        return dict(rtol=1e-5, atol=1e-5)
+    return dict(rtol=0, atol=0)
+
+
+def _check_status(status):
+    assert int(status[:, 0].abs().sum()) == 0, f"kernel reported a failure: {status.tolist()}"
+
+
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot", "hier"])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_allreduce_fp32_sizes(C, algo, world):
+    _need_gpu()
+    for n in (1, 5, 64, 1000, 4099, 262144 + 3):
+        ins = _make(world, n, torch.float32, seed=n)
+        expect = _ref(ins, "sum")
+        outs, status = C.emulated_collective("allreduce", [t.clone() for t in ins], world,
+                                             algo=algo, blocks=4, half_bytes=64 << 20 if algo == "oneshot" else 1 << 20)
+        torch.cuda.synchronize()
+        _check_status(status)
+        for r in range(world):
+            torch.testing.assert_close(outs[r].double(), expect, rtol=1e-5, atol=1e-5)
+            assert torch.equal(outs[r], outs[0]), "ranks must agree bit for bit"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("op", ["sum", "max", "min"])
+def test_allreduce_dtypes_ops(C, dtype, op):
+    _need_gpu()
+    world = 4
+    for algo in ("oneshot", "twoshot"):
+        for n in (3, 1025, 70001):
+            ins = _make(world, n, dtype, seed=7)
+            expect = _ref(ins, op)
+            outs, status = C.emulated_collective("allreduce", [t.clone() for t in ins], world,
+                                                 op=op, algo=algo, blocks=3,
+                                                 half_bytes=8 << 20)
+            torch.cuda.synchronize()
+            _check_status(status)
+            for r in range(world):
+                torch.testing.assert_close(outs[r].double(), expect, **_tol(dtype, world))
+
+
+@pytest.mark.parametrize("gpm,favorable", [(1, False), (2, False), (2, True), (4, False), (4, True), (8, False)])
+def test_allreduce_hierarchical_groupings(C, gpm, favorable):
+    _need_gpu()
+    world = 8
+    for n in (17, 50_000, 300_003):
+        ins = _make(world, n, torch.float32, seed=gpm)
+        expect = _ref(ins, "sum")
+        outs, status = C.emulated_collective("allreduce", [t.clone() for t in ins], gpm,
+                                             favorable=favorable, algo="hier", blocks=4,
+                                             half_bytes=512 << 10)  # forces several slices
+        torch.cuda.synchronize()
+        _check_status(status)
+        for r in range(world):
+            torch.testing.assert_close(outs[r].double(), expect, rtol=1e-5, atol=1e-5)
+            assert torch.equal(outs[r], outs[0])
+
+
+@pytest.mark.parametrize("wire", [torch.bfloat16, torch.float16])
+def test_allreduce_fused_scale_and_wire_cast(C, wire):
+    _need_gpu()
+    world = 8
+    n = 100_003
+    ins = _make(world, n, torch.float32, seed=3)
+    expect = torch.stack([(t.double() / world).to(wire).double() for t in ins]).sum(0)
+    for algo in ("oneshot", "twoshot", "hier"):
+        outs, status = C.emulated_collective("allreduce", [t.clone() for t in ins], world,
+                                             scale=1.0 / world, wire_dtype=wire, algo=algo,
+                                             blocks=4, half_bytes=16 << 20)
+        torch.cuda.synchronize()
+        _check_status(status)
+        for r in range(world):
+            assert outs[r].dtype == torch.float32
+            torch.testing.assert_close(outs[r].double(), expect, rtol=2e-2, atol=2e-2)
+
+
+def test_allreduce_misaligned_tensor(C):
+    """Tensors that do not start on a 16-byte boundary take the element-wise path."""
+    _need_gpu()
+    world = 4
+    for dtype in (torch.float32, torch.bfloat16, torch.uint8):
+        ins = _make(world, 10_001, dtype, seed=5)
+        expect = _ref(ins, "sum")
+        for algo in ("oneshot", "twoshot"):
+            views = []
+            for t in ins:
+                buf = torch.empty(t.numel() + 1, dtype=dtype, device="cuda")
+                v = buf[1:]  # data_ptr is off by one element
+                v.copy_(t)
+                assert v.data_ptr() % 16 != 0
+                views.append(v)
+            outs, status = C.emulated_collective("allreduce", views, world, algo=algo, blocks=2,
+                                                 half_bytes=4 << 20)
+            torch.cuda.synchronize()
+            _check_status(status)
+            for r in range(world):
+                torch.testing.assert_close(outs[r].double(), expect, **_tol(dtype, world))
+
+
+def test_repeats_exercise_both_halves_and_epochs(C):
+    _need_gpu()
+    world = 4
+    n = 40_000
+    ins = _make(world, n, torch.float32, seed=11)
+    expect = _ref(ins, "sum")
+    for algo in ("oneshot", "twoshot", "hier"):
+        reps = 5
+        outs, status = C.emulated_collective("allreduce", [t.clone() for t in ins], 2 if algo == "hier" else world,
+                                             algo=algo, blocks=4, half_bytes=8 << 20, repeats=reps)
+        torch.cuda.synchronize()
+        _check_status(status)
+        # in place: every repetition multiplies by the world size
+        torch.testing.assert_close(outs[0].double(), expect * world ** (reps - 1), rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.parametrize("gpm,favorable", [(4, False), (2, False), (2, True), (1, False)])
+def test_reduce_scatter_and_all_gather(C, gpm, favorable):
+    _need_gpu()
+    world = 4
+    for n in (1, 6, 1237, 65_537):
+        ins = _make(world, world * n, torch.float32, seed=n)
+        expect = _ref(ins, "sum")
+        outs, status = C.emulated_collective("reduce_scatter", ins, gpm, favorable=favorable,
+                                             blocks=3, half_bytes=256 << 10)
+        torch.cuda.synchronize()
+        _check_status(status)
+        for r in range(world):
+            torch.testing.assert_close(outs[r].double(), expect[r * n:(r + 1) * n], rtol=1e-5, atol=1e-5)
+        parts = _make(world, n, torch.float32, seed=n + 1)
+        outs, status = C.emulated_collective("allgather", parts, gpm, favorable=favorable,
+                                             blocks=3, half_bytes=256 << 10)
+        torch.cuda.synchronize()
+        _check_status(status)
+        full = torch.cat(parts)
+        for r in range(world):
+            assert torch.equal(outs[r], full)
+
+
+def test_wait_runs_into_its_limit_and_reports(C):
+    """A rank whose signals go nowhere: its peers give up after the time limit,
+    record who they were waiting for, and the kernel returns normally."""
+    _need_gpu()
+    world = 4
+    ins = _make(world, 10_000, torch.float32)
+    outs, status = C.emulated_collective("allreduce", [t.clone() for t in ins], world,
+                                         algo="twoshot", blocks=2, half_bytes=1 << 20,
+                                         timeout_ms=50, silent_rank=2)
+    torch.cuda.synchronize()
+    st = status.tolist()
+    for r in (0, 1, 3):
+        assert st[r][0] == 1, st  # timeout
+        assert st[r][2] == 2, st  # ... waiting for rank 2
+    # the GPU is still usable afterwards
+    x = torch.ones(10, device="cuda")
+    assert float(x.sum()) == 10.0
+    outs, status = C.emulated_collective("allreduce", [t.clone() for t in ins], world,
+                                         algo="twoshot", blocks=2, half_bytes=1 << 20)
+    _check_status(status)
+
+
+def test_fused_adamw_matches_torch(C):
+    _need_gpu()
+    torch.manual_seed(0)
+    n = 1_000_003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    ref_p = torch.nn.Parameter(p.clone())
+    ref_p.grad = g.clone()
+    opt = torch.optim.AdamW([ref_p], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m = torch.zeros_like(p)
+    v = torch.zeros_like(p)
+    for step in range(1, 4):
+        opt.step()
+        C.adamw_flat_(p, g, m, v, 1e-3, 0.9, 0.95, 1e-8, 0.1, step, 1.0)
+    torch.testing.assert_close(p, ref_p.data, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(C.sumsq(g), (g.double() ** 2).sum().float().reshape(1), rtol=1e-4, atol=0)
+
+
+def test_launch_counter_counts(C):
+    _need_gpu()
+    before = C.launch_count()
+    x = torch.randn(1024, device="cuda")
+    C.sumsq(x)
+    assert C.launch_count() == before + 1
