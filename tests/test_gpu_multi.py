@@ -1,0 +1,193 @@
+"""The backend on real GPUs, one process per GPU (needs at least two).
+
+Each configuration spawns the ranks once and runs the whole battery of checks
+inside them: all_reduce over sizes / dtypes / ops against seeded expectations,
+reduce_scatter and all_gather, the fused-scale hook, delegation to NCCL, and
+gradient parity of FlatDataParallel and of torch DDP on this backend with torch
+DDP on NCCL.
+"""
+
+import os
+
+import pytest
+import torch
+
+from _mp import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _suite(rank, world, check_ddp):
+    import torch.distributed as dist
+
+    import fairring
+    import fairring_b200
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    from datetime import timedelta
+
+    # A short group timeout: if one rank dies during set-up the others give up soon.
+    dist.init_process_group("fairring", rank=rank, world_size=world, timeout=timedelta(seconds=90))
+    be = fairring.get_backend(device="cuda")
+    report = {}
+
+    def seeded(n, dtype, r, salt=0):
+        g = torch.Generator().manual_seed(1000 * salt + r)
+        if dtype.is_floating_point:
+            return torch.randn(n, generator=g).to(dtype)
+        return torch.randint(0, 9, (n,), generator=g).to(dtype)
+
+    # all_reduce: sizes x dtypes x ops
+    for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.int32, torch.float64, torch.uint8):
+        for n in (1, 33, 4099, 262_147, 3_000_001):
+            for op in ("SUM", "MAX"):
+                if op == "MAX" and n > 5000:
+                    continue
+                t = seeded(n, dtype, rank, n).to(dev)
+                dist.all_reduce(t, op=getattr(dist.ReduceOp, op))
+                st = torch.stack([seeded(n, dtype, r, n).double() for r in range(world)])
+                expect = st.sum(0) if op == "SUM" else st.max(0).values
+                tol = 5e-2 * world if dtype in (torch.float16, torch.bfloat16) else (1e-4 if dtype.is_floating_point else 0)
+                torch.testing.assert_close(t.double().cpu(), expect, rtol=tol, atol=tol)
+    # AVG and a big buffer (many slices, several channels)
+    big = torch.full((40_000_003,), float(rank + 1), device=dev)
+    dist.all_reduce(big, op=dist.ReduceOp.AVG)
+    torch.testing.assert_close(big[:: 1_000_003].cpu(),
+                               torch.full_like(big[:: 1_000_003].cpu(), (world + 1) / 2))
+    # several collectives in flight, waited at the end
+    bufs = [torch.full((2_000_000 + i,), float(rank + i), device=dev) for i in range(12)]
+    works = [dist.all_reduce(b, async_op=True) for b in bufs]
+    for w in works:
+        w.wait()
+    for i, b in enumerate(bufs):
+        assert float(b[0]) == sum(r + i for r in range(world)) and float(b[-1]) == float(b[0])
+
+    # fused scale + bf16 wire
+    g = seeded(1_000_003, torch.float32, rank, 77).to(dev)
+    be.allreduce_fused(g, 1.0 / world, torch.bfloat16, "sum").wait()
+    expect = torch.stack([(seeded(1_000_003, torch.float32, r, 77).double() / world).bfloat16().double()
+                          for r in range(world)]).sum(0)
+    torch.testing.assert_close(g.double().cpu(), expect, rtol=2e-2, atol=2e-2)
+
+    # reduce_scatter / all_gather (tensor and list forms)
+    n = 70_001
+    inp = torch.arange(world * n, dtype=torch.float32, device=dev) * (rank + 1)
+    out = torch.empty(n, device=dev)
+    dist.reduce_scatter_tensor(out, inp)
+    torch.testing.assert_close(out.cpu(), torch.arange(world * n, dtype=torch.float32)[rank * n:(rank + 1) * n]
+                               * sum(range(1, world + 1)))
+    ag = torch.empty(world * n, device=dev)
+    dist.all_gather_into_tensor(ag, torch.full((n,), float(rank), device=dev))
+    assert torch.equal(ag.cpu(), torch.arange(world).repeat_interleave(n).float())
+    outs = [torch.empty(7, device=dev) for _ in range(world)]
+    dist.all_gather(outs, torch.full((7,), float(rank * 3), device=dev))
+    for r in range(world):
+        assert float(outs[r][0]) == r * 3
+    o = torch.empty(5, device=dev)
+    dist.reduce_scatter(o, [torch.full((5,), float(rank + i), device=dev) for i in range(world)])
+    assert float(o[0]) == sum(r + rank for r in range(world))
+
+    # delegated ops run on NCCL
+    b = torch.full((4,), float(rank), device=dev)
+    dist.broadcast(b, src=world - 1)
+    assert float(b[0]) == world - 1
+    p = torch.full((3,), 2.0, device=dev)
+    dist.all_reduce(p, op=dist.ReduceOp.PRODUCT)
+    assert float(p[0]) == 2.0 ** world
+    dist.barrier()
+
+    if check_ddp:
+        from torch.nn.parallel import DistributedDataParallel as DDP
+
+        from fairring_b200.models import DecoderConfig, DecoderLM
+        from fairring_b200.parallel import FlatDataParallel, FusedHookState, fused_allreduce_hook
+
+        cfg = DecoderConfig.tiny()
+        torch.manual_seed(0)
+        base = DecoderLM(cfg).to(dev)
+        state = {k: v.clone() for k, v in base.state_dict().items()}
+        tok = torch.randint(0, cfg.vocab, (4, cfg.seq_len + 1), generator=torch.Generator().manual_seed(rank)).to(dev)
+
+        def grads_of(wrapper_fn):
+            m = DecoderLM(cfg).to(dev)
+            m.load_state_dict(state)
+            w = wrapper_fn(m)
+            loss = w(tok[:, :-1], tok[:, 1:])
+            loss.backward()
+            torch.cuda.synchronize()
+            if isinstance(w, FlatDataParallel):
+                return [g.clone() for g in w.grads()]  # backward (reverse registration) order
+            return [p.grad.clone() for p in m.parameters()]
+
+        nccl_pg = dist.new_group(backend="nccl")
+        ref = grads_of(lambda m: DDP(m, device_ids=[rank], process_group=nccl_pg))
+        drop_in = grads_of(lambda m: DDP(m, device_ids=[rank]))
+        for a, b_ in zip(ref, drop_in):
+            torch.testing.assert_close(a, b_, rtol=1e-4, atol=1e-6)
+
+        def hooked(m):
+            d = DDP(m, device_ids=[rank])
+            d.register_comm_hook(FusedHookState(), fused_allreduce_hook)
+            return d
+
+        fused = grads_of(hooked)
+        for a, b_ in zip(ref, fused):
+            torch.testing.assert_close(a, b_, rtol=1e-4, atol=1e-6)
+        flat = grads_of(lambda m: FlatDataParallel(m, bucket_cap_mb=0.25))
+        ref_rev = list(reversed(ref))
+        for i, a in enumerate(ref_rev):
+            torch.testing.assert_close(a, flat[i], rtol=1e-4, atol=1e-6)
+        report["ddp"] = "ok"
+
+    be.check_health()
+    report["stats"] = be.stats()
+    report["describe"] = be.describe()
+    dist.destroy_process_group()
+    return report
+
+
+CONFIGS = {
+    "auto": {},
+    "twoshot_no_nvls": {"FAIRRING_NVLS": "off", "FAIRRING_ALGO": "twoshot"},
+    "nvls": {"FAIRRING_ALGO": "nvls"},
+    "nvls_oneshot": {"FAIRRING_ALGO": "nvls_oneshot"},
+    "hier_three_kernels": {"FAIRRING_ALGO": "hier", "FAIRRING_NVLS": "off"},
+    "ipc_transport_cmd_thread": {"FAIRRING_TRANSPORT": "ipc", "FAIRRING_COMMAND_THREAD": "1"},
+    "machines_of_one_gpu": {"FAIRRING_GPUS_PER_MACHINE": "1", "FAIRRING_NVLS": "off"},
+}
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_backend_on_gpus(name):
+    if _ngpu() < 2:
+        pytest.skip("needs at least two GPUs")
+    world = 2 if _ngpu() < 4 else 4
+    env = dict(CONFIGS[name])
+    env.setdefault("FAIRRING_TOTAL_MEMORY", str(64 << 20))
+    env["FAIRRING_DEVICE_TIMEOUT_MS"] = "20000"
+    res = run_ranks(_suite, world, env=env, args=(name == "auto",), timeout=600)
+    stats = res[0]["stats"]
+    assert stats["gpu_collectives"] > 50
+    if name == "twoshot_no_nvls":
+        assert stats["nvls"] == 0 and stats["launch_twoshot_allreduce"] > 0
+    if name in ("nvls", "nvls_oneshot") and stats["nvls"] == 1:
+        assert stats["launch_nvls_allreduce"] + stats["launch_nvls_oneshot_allreduce"] > 0
+    if name == "hier_three_kernels":
+        assert stats["launch_rs_intragroup"] > 0 and stats["launch_ag_intragroup"] > 0
+    if name == "machines_of_one_gpu":
+        assert stats["launch_shard_server_reduce"] > 0
+
+
+@pytest.mark.parametrize("gpm,layout", [(2, "standard"), (2, "favorable"), (4, "standard"), (1, "favorable")])
+def test_groupings_on_8_gpus(gpm, layout):
+    if _ngpu() < 8:
+        pytest.skip("needs eight GPUs")
+    env = {"FAIRRING_GPUS_PER_MACHINE": str(gpm), "FAIRRING_RANK_LAYOUT": layout,
+           "FAIRRING_TOTAL_MEMORY": str(64 << 20), "FAIRRING_DEVICE_TIMEOUT_MS": "20000"}
+    res = run_ranks(_suite, 8, env=env, args=(False,), timeout=900)
+    assert res[0]["stats"]["launch_shard_server_reduce"] > 0
