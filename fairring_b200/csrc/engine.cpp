@@ -57,6 +57,17 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
   FR_CHECK(cfg_.blocks >= 1 && cfg_.blocks <= kMaxBlocks, "FAIRRING_BLOCKS must be in 1..",
            kMaxBlocks);
   FR_CUDA(cudaSetDevice(device_));
+  // Kernels of different channels wait on their peers while resident.  If more
+  // blocks were in flight than the GPU can hold at once, two GPUs could each
+  // keep resident exactly the blocks whose partners are still queued on the
+  // other GPU, and nobody would move.  So: (channels x blocks) never exceeds
+  // the SM count.  The kernels are built for two resident blocks per SM
+  // (__launch_bounds__(512, 2)), which leaves the other half of every SM to
+  // the compute kernels the collectives overlap with, or to a second engine.
+  int sms = 0;
+  FR_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_));
+  const int max_channels = std::max(1, sms / cfg_.blocks);
+  if (cfg_.parallelism > max_channels) cfg_.parallelism = max_channels;
   plan_ = planMemory(cfg_.total_memory, cfg_.slice_bytes, cfg_.parallelism, topo_.world,
                      cfg_.min_half_bytes);
 

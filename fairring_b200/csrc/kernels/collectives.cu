@@ -33,7 +33,7 @@ namespace {
 
 using namespace dev;
 
-constexpr int kU = 2;                      // vectors per thread per tile
+constexpr int kU = 1;                      // vectors per thread per tile
 constexpr int kTile = kThreads * kU;       // vectors per tile
 
 enum BarrierKind { kAll = 0, kGroup = 1, kRail = 2 };
@@ -601,12 +601,12 @@ __device__ __forceinline__ void body(const ChannelDev& c, const OpArgs& a) {
 // One __global__ per kernel id so that profiles show the stage by name.
 #define FR_DEFINE_KERNEL(NAME, KID)                                                         \
   template <typename IO, typename WIRE>                                                     \
-  __global__ void __launch_bounds__(kThreads, 1)                                            \
+  __global__ void __launch_bounds__(kThreads, 2)                                            \
       NAME(const __grid_constant__ ChannelDev c, const __grid_constant__ OpArgs a) {        \
     body<IO, WIRE, KID>(c, a);                                                              \
   }                                                                                         \
   template <typename IO, typename WIRE>                                                     \
-  __global__ void __launch_bounds__(kThreads, 1)                                            \
+  __global__ void __launch_bounds__(kThreads, 2)                                            \
       NAME##_emulated(const ChannelDev* cs, const OpArgs* as) {                             \
     body<IO, WIRE, KID>(cs[blockIdx.y], as[blockIdx.y]);                                    \
   }

@@ -29,6 +29,18 @@ def _child(fn, rank, world, port, env, q, args):
         q.put((rank, "ok", out))
     except BaseException as e:  # noqa: BLE001 - report everything to the parent
         q.put((rank, "error", f"{type(e).__name__}: {e}\n{traceback.format_exc()}"))
+    finally:
+        # Make sure the report has left this process before anything at
+        # interpreter exit can go wrong.
+        q.close()
+        q.join_thread()
+        try:
+            import torch.distributed as dist
+
+            if dist.is_initialized():
+                dist.destroy_process_group()
+        except BaseException:  # noqa: BLE001
+            pass
 
 
 def run_ranks(fn, world: int, env: dict | None = None, args: tuple = (), timeout: float = 180.0):
@@ -44,15 +56,33 @@ def run_ranks(fn, world: int, env: dict | None = None, args: tuple = (), timeout
         p.start()
     results = {}
     errors = []
+    import queue as _queue
+    import time as _time
+
+    deadline = _time.time() + timeout
     try:
-        for _ in range(world):
-            rank, status, payload = q.get(timeout=timeout)
+        while len(results) + len(errors) < world:
+            try:
+                rank, status, payload = q.get(timeout=1.0)
+            except _queue.Empty:
+                if _time.time() > deadline:
+                    errors.append((-1, f"no report from some ranks within {timeout} s"))
+                    break
+                reported = set(results) | {r for r, _ in errors}
+                dead = [r for r, p in enumerate(procs)
+                        if not p.is_alive() and r not in reported]
+                if dead and q.empty():
+                    _time.sleep(1.0)  # a last report may still be in the pipe
+                    if q.empty():
+                        errors.append((dead[0], f"process exited with code {procs[dead[0]].exitcode} "
+                                                "without reporting"))
+                        break
+                continue
             if status == "ok":
                 results[rank] = payload
             else:
                 errors.append((rank, payload))
-    except Exception as e:  # queue.Empty: somebody never reported
-        errors.append((-1, f"timeout waiting for ranks: {e!r}"))
+                break  # the others may now be stuck waiting for this rank
     finally:
         for p in procs:
             p.join(timeout=10)

@@ -169,8 +169,8 @@ def test_backend_on_gpus(name):
     world = 2 if _ngpu() < 4 else 4
     env = dict(CONFIGS[name])
     env.setdefault("FAIRRING_TOTAL_MEMORY", str(64 << 20))
-    env["FAIRRING_DEVICE_TIMEOUT_MS"] = "20000"
-    res = run_ranks(_suite, world, env=env, args=(name == "auto",), timeout=600)
+    env["FAIRRING_DEVICE_TIMEOUT_MS"] = "5000"
+    res = run_ranks(_suite, world, env=env, args=(name == "auto",), timeout=240)
     stats = res[0]["stats"]
     assert stats["gpu_collectives"] > 50
     if name == "twoshot_no_nvls":
