@@ -31,6 +31,16 @@ SOURCES = [
     "bench_client.cpp",
     "local_ops.cpp",
     "kernels/collectives.cu",
+    "kernels/collectives_u8.cu",
+    "kernels/collectives_i8.cu",
+    "kernels/collectives_i32.cu",
+    "kernels/collectives_i64.cu",
+    "kernels/collectives_f16.cu",
+    "kernels/collectives_bf16.cu",
+    "kernels/collectives_f32.cu",
+    "kernels/collectives_f64.cu",
+    "kernels/collectives_f32_bf16.cu",
+    "kernels/collectives_f32_f16.cu",
     "kernels/local_ops.cu",
 ]
 

@@ -151,6 +151,12 @@ void BackendFairring::shutdown() {
   std::lock_guard<std::mutex> lk(mu_);
   engine_.reset();
   cpu_engine_.reset();
+  for (auto& kv : delegates_) {
+    try {
+      kv.second->shutdown();
+    } catch (...) {
+    }
+  }
   delegates_.clear();
 }
 

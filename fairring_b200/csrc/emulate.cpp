@@ -107,33 +107,27 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
   }
   const Topo t0 = chs[0].topo;
   at::Tensor chs_dev = at::empty({(int64_t)(sizeof(ChannelDev) * W)}, u8);
-  at::Tensor args_dev = at::empty({(int64_t)(sizeof(OpArgs) * W)}, u8);
   FR_CUDA(cudaMemcpyAsync(chs_dev.data_ptr(), chs.data(), sizeof(ChannelDev) * W,
                           cudaMemcpyHostToDevice, stream));
 
   auto launchAll = [&](KernelId id, const Seg& seg, int64_t in_off, int64_t out_off, uint32_t fl) {
-    std::vector<OpArgs> as(W);
     const int ies = dtypeSize(io);
+    OpArgs a;
+    std::memset(&a, 0, sizeof(a));
     for (int r = 0; r < W; ++r) {
-      OpArgs& a = as[r];
-      std::memset(&a, 0, sizeof(a));
-      a.in = static_cast<const char*>(inputs[r].data_ptr()) + in_off * ies;
-      a.out = static_cast<char*>(outs[r].data_ptr()) + out_off * ies;
-      a.seg = seg;
-      a.scale = (float)scale;
-      a.op = (int32_t)rop;
-      a.io_dtype = (int32_t)io;
-      a.wire_dtype = (int32_t)wire;
-      a.flags = fl;
+      a.in[r] = static_cast<const char*>(inputs[r].data_ptr()) + in_off * ies;
+      a.out[r] = static_cast<char*>(outs[r].data_ptr()) + out_off * ies;
     }
-    FR_CUDA(cudaMemcpyAsync(args_dev.data_ptr(), as.data(), sizeof(OpArgs) * W,
-                            cudaMemcpyHostToDevice, stream));
-    cudaError_t e = launchEmulated(id, static_cast<const ChannelDev*>(chs_dev.data_ptr()),
-                                   static_cast<const OpArgs*>(args_dev.data_ptr()), W, (int)blocks,
-                                   stream);
+    a.seg = seg;
+    a.scale = (float)scale;
+    a.op = (int32_t)rop;
+    a.io_dtype = (int32_t)io;
+    a.wire_dtype = (int32_t)wire;
+    a.flags = fl;
+    cudaError_t e = launchEmulated(id, static_cast<const ChannelDev*>(chs_dev.data_ptr()), a, W,
+                                   (int)blocks, stream);
     TORCH_CHECK(e == cudaSuccess, "emulated launch of ", kernelName(id), " failed: ",
                 cudaGetErrorString(e));
-    FR_CUDA(cudaStreamSynchronize(stream));  // args_dev is reused by the next launch
   };
 
   for (int64_t rep = 0; rep < repeats; ++rep) {

@@ -109,6 +109,11 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
     ch.dev.timeout_ns = cfg_.device_timeout_ns;
     ch.dev.topo = topo_;
   }
+  // The kernels read the channel description from device memory.
+  FR_CUDA(cudaMalloc(&channels_dev_, sizeof(ChannelDev) * plan_.channels));
+  for (int c = 0; c < plan_.channels; ++c)
+    FR_CUDA(cudaMemcpy(channels_dev_ + c, &channels_[c].dev, sizeof(ChannelDev),
+                       cudaMemcpyHostToDevice));
   events_.resize(kEventPool);
   for (auto& e : events_) FR_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   FR_CUDA(cudaDeviceSynchronize());
@@ -138,12 +143,18 @@ Engine::~Engine() {
   } catch (const std::exception&) {
   }
   for (auto& ch : channels_) {
-    if (ch.stream) cudaStreamDestroy(ch.stream);
+    // The side streams are deliberately never destroyed.  Tensors that were
+    // used on them carry a record of that in the caching allocator, which will
+    // record an event on the stream when such a tensor is finally freed --
+    // possibly long after this engine is gone.  A destroyed stream there means
+    // an exception from inside a destructor.  (The reference leaks its merge
+    // streams for the same reason, fairring/machine.cc:162-175.)
     if (ch.done) cudaEventDestroy(ch.done);
   }
   for (auto& e : events_)
     if (e) cudaEventDestroy(e);
   if (seq_dev_) cudaFree(seq_dev_);
+  if (channels_dev_) cudaFree(channels_dev_);
   if (status_host_) cudaFreeHost(status_host_);
 }
 
@@ -251,7 +262,8 @@ Algo Engine::chooseAllreduce(int64_t wire_bytes, DType wire, RedOp op) const {
 }
 
 void Engine::launch(Channel& ch, KernelId id, const OpArgs& a) {
-  cudaError_t e = launchCollective(id, ch.dev, a, cfg_.blocks, ch.stream);
+  cudaError_t e = launchCollective(id, channels_dev_ + (&ch - channels_.data()), a, cfg_.blocks,
+                                   ch.stream);
   FR_CHECK(e == cudaSuccess, "launch of ", kernelName(id), " failed: ", cudaGetErrorString(e));
   ++stats_.launches[(size_t)id];
 }
@@ -259,8 +271,8 @@ void Engine::launch(Channel& ch, KernelId id, const OpArgs& a) {
 void Engine::runAllreduceSlice(Channel& ch, const CollectiveDesc& d, const void* in, void* out,
                                int64_t n, Algo algo) {
   OpArgs a{};
-  a.in = in;
-  a.out = out;
+  a.in[0] = in;
+  a.out[0] = out;
   a.seg = allreduceSeg(n, dtypeSize(d.wire), topo_.world);
   a.scale = d.scale;
   a.op = (int32_t)d.op;
@@ -339,8 +351,8 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after) {
     for (int64_t off = 0; off < d.numel; off += max_len) {
       const int64_t len = std::min(max_len, d.numel - off);
       OpArgs a{};
-      a.in = in + off * ies;
-      a.out = out + off * ies;
+      a.in[0] = in + off * ies;
+      a.out[0] = out + off * ies;
       a.seg = scatterSeg(len, d.numel, wes);
       a.scale = d.scale;
       a.op = (int32_t)d.op;

@@ -140,6 +140,7 @@ class Engine {
   uint32_t* status_host_ = nullptr;  // pinned + mapped: [channels][kStatusWords], then abort word
   uint32_t* status_dev_ = nullptr;
   std::vector<Channel> channels_;
+  ChannelDev* channels_dev_ = nullptr;  // device copy of channels_[i].dev
   std::vector<cudaEvent_t> events_;
   size_t next_event_ = 0;
   uint64_t next_channel_ = 0;

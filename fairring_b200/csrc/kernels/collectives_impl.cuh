@@ -1,0 +1,787 @@
+// The collective kernels (sm_100a).  Each kernel is a short sequence of
+// "phases" separated by flag barriers between the same-numbered blocks of the
+// participating GPUs.  A phase moves 16-byte vectors between the user's tensor,
+// this GPU's staging slot and the peers' staging slots (mapped peer memory over
+// NVLink, or the NVSwitch multicast address for the NVLS variants).
+//
+// Work split: a chunk of qv vectors is cut into tiles of kTile vectors; block b
+// owns tiles b, b+G, ...  The split is the same in every phase and on every
+// rank, so the data block b reads after a barrier was written by block b of
+// the peer before that barrier: block-to-block flags are enough and no
+// grid-wide synchronisation is needed inside a kernel.  Between kernels of one
+// channel the stream order of the peer does the rest (a peer's block can only
+// signal from kernel k+1 once its kernel k has finished).
+//
+// Staging reuse: consecutive collectives of a channel use alternate halves of
+// the slot and the first barrier of every collective spans all ranks; having
+// passed it proves that every peer finished the collective before, so the half
+// used two collectives ago is free again without a trailing barrier.
+//
+// Reference behaviour covered: fairring/device.cc:33-209 (the five stage
+// primitives) and :444-753 (their per-slice composition).
+
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "device_prims.cuh"
+#include "kernels.h"
+
+namespace fairring {
+namespace impl {
+
+using namespace dev;
+
+
+enum BarrierKind { kAll = 0, kGroup = 1, kRail = 2 };
+
+struct BlockCtx {
+  uint32_t seq;     // collectives this block has completed on this channel
+  uint64_t half;    // byte offset of the half-slot in use
+  int b;            // block index within the rank
+  int G;            // blocks per rank
+};
+
+// Arrive at barrier `idx` of the current collective and wait for the peers of
+// the given kind.  Returns false if a wait gave up; the reason is then in the
+// status words and the caller must leave the kernel.
+template <int KIND>
+__device__ __forceinline__ bool barrier(const ChannelDev& c, const BlockCtx& bc, int idx) {
+  const Topo& t = c.topo;
+  const uint32_t epoch = bc.seq * (uint32_t)kBarriersPerOp + (uint32_t)idx + 1u;
+  const int n = KIND == kAll ? t.world : (KIND == kGroup ? t.D : t.M);
+  __syncthreads();
+  uint32_t st = kStatusOk;
+  int peer = -1;
+  if ((int)threadIdx.x < n) {
+    const int i = threadIdx.x;
+    peer = KIND == kAll ? i : (KIND == kGroup ? rankOf(t, t.m, i) : rankOf(t, i, t.d));
+    if (peer != t.rank) {
+      __threadfence_system();
+      stReleaseSys(c.flags[peer] + t.rank * kMaxBlocks + bc.b, epoch);
+      st = waitFlag(c.flags[t.rank] + peer * kMaxBlocks + bc.b, epoch, c.timeout_ns,
+                    c.abort_flag);
+      if (st != kStatusOk) {
+        volatile uint32_t* s = c.status;
+        s[1] = (uint32_t)idx;
+        s[2] = (uint32_t)peer;
+        s[3] = bc.seq;
+        __threadfence_system();
+        s[0] = st;
+      }
+    }
+  }
+  return __syncthreads_or(st != kStatusOk) == 0;
+}
+
+__device__ __forceinline__ BlockCtx enter(const ChannelDev& c) {
+  BlockCtx bc;
+  bc.b = blockIdx.x;
+  bc.G = gridDim.x;
+  bc.seq = c.seq[bc.b];  // written only by this block, at the end of a kernel
+  bc.half = (bc.seq & 1u) ? c.half_bytes : 0;
+  return bc;
+}
+
+__device__ __forceinline__ void leave(const ChannelDev& c, const OpArgs& a, const BlockCtx& bc) {
+  __syncthreads();
+  if ((a.flags & kAdvanceSeq) && threadIdx.x == 0) c.seq[bc.b] = bc.seq + 1u;
+}
+
+__device__ __forceinline__ char* stageAt(char* slot, uint64_t half, int64_t vec) {
+  return slot + half + (uint64_t)vec * kVecBytes;
+}
+
+template <typename IO>
+__device__ __forceinline__ bool chunkAligned(const IO* base, const Seg& s, int c) {
+  return ((reinterpret_cast<uintptr_t>(base + (int64_t)c * s.chunk_stride)) & 15u) == 0;
+}
+
+// Scale (floating accumulators only) while the data is first read.
+template <typename A, int V>
+__device__ __forceinline__ void applyScale(A (&a)[V], float scale) {
+  if constexpr (std::is_floating_point<A>::value) {
+    if (scale != 1.0f) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) a[i] = a[i] * (A)scale;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Work split.  A chunk of qv vectors is cut into tiles of kThreads vectors;
+// block b owns tiles b, b+G, b+2G, ...  A thread works on U of its block's
+// tiles at a time so that U (times the number of peers) 16-byte accesses are
+// in flight per thread; U differs between phases, ownership never does.
+// ---------------------------------------------------------------------------
+template <int U>
+struct Batch {
+  int64_t v[U];
+  bool ok[U];
+};
+template <int U>
+__device__ __forceinline__ Batch<U> batchAt(int64_t tile0, const BlockCtx& bc, int64_t ntiles,
+                                            int64_t qv) {
+  Batch<U> t;
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int64_t tile = tile0 + (int64_t)u * bc.G;
+    t.v[u] = tile * kThreads + threadIdx.x;
+    t.ok[u] = tile < ntiles && t.v[u] < qv;
+  }
+  return t;
+}
+
+// Pick the unroll U and the static bound KP on the number of peers so that a
+// batch keeps at most 16 sixteen-byte words live: `peers` accesses per vector,
+// `nv` words per access.
+#define FR_WITH_UNROLL(peers, nv, ...)          \
+  do {                                          \
+    if ((peers) * (nv) <= 4) {                  \
+      constexpr int U = 4;                      \
+      constexpr int KP = 4 / (nv);              \
+      __VA_ARGS__;                              \
+    } else if ((peers) * (nv) <= 8) {           \
+      constexpr int U = 2;                      \
+      constexpr int KP = 8 / (nv);              \
+      __VA_ARGS__;                              \
+    } else {                                    \
+      constexpr int U = 1;                      \
+      constexpr int KP = kMaxRanks;             \
+      __VA_ARGS__;                              \
+    }                                           \
+  } while (0)
+
+// V elements of the user's tensor.  When the vector is whole and 16-byte
+// aligned ("fast") its raw words are loaded first and converted after all
+// loads of the batch have been issued; otherwise it is read element by element
+// at conversion time.  Only the raw words stay live across the batch.
+template <typename IO, int V>
+struct UserRaw {
+  uint4 w[V * sizeof(IO) / 16];
+};
+template <typename IO, int V>
+__device__ __forceinline__ void userIssue(UserRaw<IO, V>& r, const IO* p, bool fast) {
+  if (fast) {
+#pragma unroll
+    for (int k = 0; k < (int)(V * sizeof(IO) / 16); ++k) r.w[k] = reinterpret_cast<const uint4*>(p)[k];
+  }
+}
+template <typename IO, int V>
+__device__ __forceinline__ void userFinish(const UserRaw<IO, V>& r, const IO* p, int nvalid,
+                                           bool fast, typename Tr<IO>::Acc (&x)[V]) {
+  if (fast) {
+    const IO* e = reinterpret_cast<const IO*>(r.w);
+#pragma unroll
+    for (int i = 0; i < V; ++i) x[i] = Tr<IO>::up(e[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) x[i] = i < nvalid ? Tr<IO>::up(p[i]) : typename Tr<IO>::Acc(0);
+  }
+}
+
+template <typename IO, typename WIRE, int V>
+__device__ __forceinline__ void storeUserFromWire(IO* p, int nvalid, bool aligned, const uint4& w) {
+  typename Tr<WIRE>::Acc x[V];
+  unpack<WIRE, V>(w, x);
+  typename Tr<IO>::Acc y[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) y[i] = (typename Tr<IO>::Acc)x[i];
+  storeUser<IO, V>(p, nvalid, aligned, y);
+}
+
+// ---------------------------------------------------------------------------
+// Phase: push.  Read the user's input once and store rail chunk j destined to
+// group member d' into slot d of that member's staging (scaled, cast to the
+// wire type).  With M == 1 this is "chunk p goes to rank p".
+// ---------------------------------------------------------------------------
+template <typename IO, typename WIRE, int U, int KP>
+__device__ __forceinline__ void phasePushU(const ChannelDev& c, const OpArgs& a,
+                                           const BlockCtx& bc) {
+  constexpr int V = kVecBytes / sizeof(WIRE);
+  using Acc = typename Tr<IO>::Acc;
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  const IO* in = static_cast<const IO*>(a.in[blockIdx.y]);
+  const int64_t ntiles = ceilDiv(s.qv, kThreads);
+  for (int j = 0; j < t.M; ++j) {
+    for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+      const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, s.qv);
+      UserRaw<IO, V> raw[U][KP];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+          if (k < t.D && tb.ok[u]) {
+            const int dd = (t.d + 1 + k) % t.D;  // start at the neighbour: spreads the links
+            const int chunk = rankOf(t, j, dd);
+            const bool fast = chunkAligned(in, s, chunk) && validInVector(s, chunk, tb.v[u], V) == V;
+            userIssue<IO, V>(raw[u][k], in + (int64_t)chunk * s.chunk_stride + tb.v[u] * V, fast);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+          if (k < t.D && tb.ok[u]) {
+            const int dd = (t.d + 1 + k) % t.D;
+            const int chunk = rankOf(t, j, dd);
+            const int nvalid = (int)validInVector(s, chunk, tb.v[u], V);
+            const bool fast = chunkAligned(in, s, chunk) && nvalid == V;
+            Acc x[V];
+            userFinish<IO, V>(raw[u][k], in + (int64_t)chunk * s.chunk_stride + tb.v[u] * V, nvalid,
+                              fast, x);
+            applyScale(x, a.scale);
+            stStage(stageAt(c.staging[rankOf(t, t.m, dd)], bc.half,
+                            stagingVec(t, s, t.d, j) + tb.v[u]),
+                    pack<WIRE, V>(x));
+          }
+        }
+      }
+    }
+  }
+}
+template <typename IO, typename WIRE>
+__device__ __forceinline__ void phasePush(const ChannelDev& c, const OpArgs& a,
+                                          const BlockCtx& bc) {
+  constexpr int NV = sizeof(IO) / sizeof(WIRE);  // 16-byte loads per vector
+  FR_WITH_UNROLL(c.topo.D, NV, phasePushU<IO, WIRE, U, KP>(c, a, bc));
+}
+
+// ---------------------------------------------------------------------------
+// Phase: local reduce.  Sum (or max/min) the D source slots of this GPU's own
+// staging, in slot order so that the result does not depend on timing; write
+// the self slot, or the user's output for a flat reduce_scatter.
+// ---------------------------------------------------------------------------
+template <typename IO, typename WIRE, int U, int KP>
+__device__ __forceinline__ void phaseLocalReduceU(const ChannelDev& c, const OpArgs& a,
+                                                  const BlockCtx& bc) {
+  constexpr int V = kVecBytes / sizeof(WIRE);
+  using Acc = typename Tr<WIRE>::Acc;
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  char* own = c.staging[t.rank];
+  const bool to_user = (a.flags & kToUser) != 0;
+  IO* out = static_cast<IO*>(a.out[blockIdx.y]);
+  const int64_t ntiles = ceilDiv(s.qv, kThreads);
+  for (int j = 0; j < t.M; ++j) {
+    for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+      const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, s.qv);
+      uint4 raw[U][KP];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int k = 0; k < KP; ++k)
+          if (k < t.D && tb.ok[u])
+            raw[u][k] = ldStage(stageAt(own, bc.half, stagingVec(t, s, k, j) + tb.v[u]));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (!tb.ok[u]) continue;
+        Acc acc[V];
+        unpack<WIRE, V>(raw[u][0], acc);
+#pragma unroll
+        for (int k = 1; k < KP; ++k) {
+          if (k < t.D) {
+            Acc x[V];
+            unpack<WIRE, V>(raw[u][k], x);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] = combine(acc[i], x[i], a.op);
+          }
+        }
+        const uint4 r = pack<WIRE, V>(acc);
+        if (to_user) {
+          // Flat reduce_scatter: this rank's chunk is its whole output.
+          const int chunk = rankOf(t, j, t.d);
+          storeUserFromWire<IO, WIRE, V>(out + tb.v[u] * V, (int)validInVector(s, chunk, tb.v[u], V),
+                                         (reinterpret_cast<uintptr_t>(out) & 15u) == 0, r);
+        } else {
+          stStage(stageAt(own, bc.half, stagingVec(t, s, t.d, j) + tb.v[u]), r);
+        }
+      }
+    }
+  }
+}
+template <typename IO, typename WIRE>
+__device__ __forceinline__ void phaseLocalReduce(const ChannelDev& c, const OpArgs& a,
+                                                 const BlockCtx& bc) {
+  FR_WITH_UNROLL(c.topo.D, 1, phaseLocalReduceU<IO, WIRE, U, KP>(c, a, bc));
+}
+
+// ---------------------------------------------------------------------------
+// Phase: shard-server reduce.  This GPU serves shard (d, m): pull the group
+// partial sums of that shard from the self slot of each rail peer (machine
+// order), reduce in registers, then either push the result back into every
+// rail peer's self slot (all_reduce: collect + add + diffuse in one pass) or
+// write the user's output (reduce_scatter).
+// ---------------------------------------------------------------------------
+template <typename IO, typename WIRE, int U, int KP>
+__device__ __forceinline__ void phaseServerReduceU(const ChannelDev& c, const OpArgs& a,
+                                                   const BlockCtx& bc) {
+  constexpr int V = kVecBytes / sizeof(WIRE);
+  using Acc = typename Tr<WIRE>::Acc;
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  const bool to_user = (a.flags & kToUser) != 0;
+  IO* out = static_cast<IO*>(a.out[blockIdx.y]);
+  const int64_t shard = stagingVec(t, s, t.d, t.m);
+  const int64_t ntiles = ceilDiv(s.qv, kThreads);
+  for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+    const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, s.qv);
+    uint4 raw[U][KP];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int k = 0; k < KP; ++k)
+        if (k < t.M && tb.ok[u])
+          raw[u][k] = ldStage(stageAt(c.staging[rankOf(t, k, t.d)], bc.half, shard + tb.v[u]));
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!tb.ok[u]) continue;
+      Acc acc[V];
+      unpack<WIRE, V>(raw[u][0], acc);
+#pragma unroll
+      for (int k = 1; k < KP; ++k) {
+        if (k < t.M) {
+          Acc x[V];
+          unpack<WIRE, V>(raw[u][k], x);
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc[i] = combine(acc[i], x[i], a.op);
+        }
+      }
+      const uint4 r = pack<WIRE, V>(acc);
+      if (to_user) {
+        storeUserFromWire<IO, WIRE, V>(out + tb.v[u] * V, (int)validInVector(s, t.rank, tb.v[u], V),
+                                       (reinterpret_cast<uintptr_t>(out) & 15u) == 0, r);
+      } else {
+#pragma unroll
+        for (int k = 0; k < KP; ++k)
+          if (k < t.M) stStage(stageAt(c.staging[rankOf(t, k, t.d)], bc.half, shard + tb.v[u]), r);
+      }
+    }
+  }
+}
+template <typename IO, typename WIRE>
+__device__ __forceinline__ void phaseServerReduce(const ChannelDev& c, const OpArgs& a,
+                                                  const BlockCtx& bc) {
+  FR_WITH_UNROLL(c.topo.M, 1, phaseServerReduceU<IO, WIRE, U, KP>(c, a, bc));
+}
+
+// ---------------------------------------------------------------------------
+// Phase: gather.  Pull the reduced rail chunks from the self slot of every
+// group member and write them (cast back) into the user's output.
+// ---------------------------------------------------------------------------
+template <typename IO, typename WIRE, int U, int KP>
+__device__ __forceinline__ void phaseGatherU(const ChannelDev& c, const OpArgs& a,
+                                             const BlockCtx& bc) {
+  constexpr int V = kVecBytes / sizeof(WIRE);
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  IO* out = static_cast<IO*>(a.out[blockIdx.y]);
+  const int64_t ntiles = ceilDiv(s.qv, kThreads);
+  for (int j = 0; j < t.M; ++j) {
+    for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+      const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, s.qv);
+      uint4 raw[U][KP];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+          if (k < t.D && tb.ok[u]) {
+            const int dd = (t.d + k) % t.D;
+            raw[u][k] = ldStage(stageAt(c.staging[rankOf(t, t.m, dd)], bc.half,
+                                        stagingVec(t, s, dd, j) + tb.v[u]));
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+          if (k < t.D && tb.ok[u]) {
+            const int dd = (t.d + k) % t.D;
+            const int chunk = rankOf(t, j, dd);
+            storeUserFromWire<IO, WIRE, V>(out + (int64_t)chunk * s.chunk_stride + tb.v[u] * V,
+                                           (int)validInVector(s, chunk, tb.v[u], V),
+                                           chunkAligned(out, s, chunk), raw[u][k]);
+          }
+        }
+      }
+    }
+  }
+}
+template <typename IO, typename WIRE>
+__device__ __forceinline__ void phaseGather(const ChannelDev& c, const OpArgs& a,
+                                            const BlockCtx& bc) {
+  FR_WITH_UNROLL(c.topo.D, 1, phaseGatherU<IO, WIRE, U, KP>(c, a, bc));
+}
+
+// ---------------------------------------------------------------------------
+// Phase: diffuse (all_gather stage 1).  The user's input is this rank's chunk;
+// store it into the self slot, rail position m, of every rail peer (self
+// included).  Afterwards every GPU's self slot holds its whole rail.
+// ---------------------------------------------------------------------------
+template <typename IO, typename WIRE, int U>
+__device__ __forceinline__ void phaseDiffuseU(const ChannelDev& c, const OpArgs& a,
+                                              const BlockCtx& bc) {
+  constexpr int V = kVecBytes / sizeof(WIRE);
+  using Acc = typename Tr<IO>::Acc;
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  const IO* in = static_cast<const IO*>(a.in[blockIdx.y]);
+  const bool aligned = (reinterpret_cast<uintptr_t>(in) & 15u) == 0;
+  const int64_t shard = stagingVec(t, s, t.d, t.m);
+  const int64_t ntiles = ceilDiv(s.qv, kThreads);
+  for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+    const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, s.qv);
+    UserRaw<IO, V> raw[U];
+    auto validAt = [&](int64_t v) {
+      const int64_t nv = s.chunk_len - v * V;
+      return nv > V ? V : (nv < 0 ? 0 : (int)nv);
+    };
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (tb.ok[u]) userIssue<IO, V>(raw[u], in + tb.v[u] * V, aligned && validAt(tb.v[u]) == V);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!tb.ok[u]) continue;
+      const int nvalid = validAt(tb.v[u]);
+      Acc x[V];
+      userFinish<IO, V>(raw[u], in + tb.v[u] * V, nvalid, aligned && nvalid == V, x);
+      applyScale(x, a.scale);
+      const uint4 r = pack<WIRE, V>(x);
+#pragma unroll
+      for (int k = 0; k < kMaxRanks; ++k)
+        if (k < t.M) stStage(stageAt(c.staging[rankOf(t, k, t.d)], bc.half, shard + tb.v[u]), r);
+    }
+  }
+}
+template <typename IO, typename WIRE>
+__device__ __forceinline__ void phaseDiffuse(const ChannelDev& c, const OpArgs& a,
+                                             const BlockCtx& bc) {
+  constexpr int NV = sizeof(IO) / sizeof(WIRE);
+  phaseDiffuseU<IO, WIRE, 4 / NV>(c, a, bc);
+}
+
+// ---------------------------------------------------------------------------
+// One-shot phases.  Staging layout of a half: [source rank][chunk][qv].
+// ---------------------------------------------------------------------------
+template <typename IO, typename WIRE, int U>
+__device__ __forceinline__ void phasePushAllU(const ChannelDev& c, const OpArgs& a,
+                                              const BlockCtx& bc) {
+  constexpr int V = kVecBytes / sizeof(WIRE);
+  using Acc = typename Tr<IO>::Acc;
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  const IO* in = static_cast<const IO*>(a.in[blockIdx.y]);
+  const int W = t.world;
+  const int64_t ntiles = ceilDiv(s.qv, kThreads);
+  for (int chunk = 0; chunk < W; ++chunk) {
+    const bool aligned = chunkAligned(in, s, chunk);
+    for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+      const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, s.qv);
+      UserRaw<IO, V> raw[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (tb.ok[u])
+          userIssue<IO, V>(raw[u], in + (int64_t)chunk * s.chunk_stride + tb.v[u] * V,
+                           aligned && validInVector(s, chunk, tb.v[u], V) == V);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (!tb.ok[u]) continue;
+        const int nvalid = (int)validInVector(s, chunk, tb.v[u], V);
+        Acc x[V];
+        userFinish<IO, V>(raw[u], in + (int64_t)chunk * s.chunk_stride + tb.v[u] * V, nvalid,
+                          aligned && nvalid == V, x);
+        applyScale(x, a.scale);
+        const uint4 r = pack<WIRE, V>(x);
+        const int64_t pos = ((int64_t)t.rank * W + chunk) * s.qv + tb.v[u];
+#pragma unroll
+        for (int k = 0; k < kMaxRanks; ++k)
+          if (k < W) stStage(stageAt(c.staging[(t.rank + k) % W], bc.half, pos), r);
+      }
+    }
+  }
+}
+template <typename IO, typename WIRE>
+__device__ __forceinline__ void phasePushAll(const ChannelDev& c, const OpArgs& a,
+                                             const BlockCtx& bc) {
+  constexpr int NV = sizeof(IO) / sizeof(WIRE);
+  phasePushAllU<IO, WIRE, 4 / NV>(c, a, bc);
+}
+
+template <typename IO, typename WIRE, int U, int KP>
+__device__ __forceinline__ void phaseReduceAllU(const ChannelDev& c, const OpArgs& a,
+                                                const BlockCtx& bc) {
+  constexpr int V = kVecBytes / sizeof(WIRE);
+  using Acc = typename Tr<WIRE>::Acc;
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  IO* out = static_cast<IO*>(a.out[blockIdx.y]);
+  char* own = c.staging[t.rank];
+  const int W = t.world;
+  const int64_t ntiles = ceilDiv(s.qv, kThreads);
+  for (int chunk = 0; chunk < W; ++chunk) {
+    const bool aligned = chunkAligned(out, s, chunk);
+    for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+      const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, s.qv);
+      uint4 raw[U][KP];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int k = 0; k < KP; ++k)
+          if (k < W && tb.ok[u])
+            raw[u][k] = ldStage(stageAt(own, bc.half, ((int64_t)k * W + chunk) * s.qv + tb.v[u]));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (!tb.ok[u]) continue;
+        Acc acc[V];
+        unpack<WIRE, V>(raw[u][0], acc);
+#pragma unroll
+        for (int k = 1; k < KP; ++k) {
+          if (k < W) {
+            Acc x[V];
+            unpack<WIRE, V>(raw[u][k], x);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] = combine(acc[i], x[i], a.op);
+          }
+        }
+        storeUserFromWire<IO, WIRE, V>(out + (int64_t)chunk * s.chunk_stride + tb.v[u] * V,
+                                       (int)validInVector(s, chunk, tb.v[u], V), aligned,
+                                       pack<WIRE, V>(acc));
+      }
+    }
+  }
+}
+template <typename IO, typename WIRE>
+__device__ __forceinline__ void phaseReduceAll(const ChannelDev& c, const OpArgs& a,
+                                               const BlockCtx& bc) {
+  FR_WITH_UNROLL(c.topo.world, 1, phaseReduceAllU<IO, WIRE, U, KP>(c, a, bc));
+}
+
+// ---------------------------------------------------------------------------
+// NVLS phases.  Staging layout of a half: [chunk][qv], one copy per GPU, all
+// copies bound to one multicast object.
+// ---------------------------------------------------------------------------
+template <typename IO, typename WIRE, int U>
+__device__ __forceinline__ void phaseCopyInU(const ChannelDev& c, const OpArgs& a,
+                                             const BlockCtx& bc) {
+  constexpr int V = kVecBytes / sizeof(WIRE);
+  using Acc = typename Tr<IO>::Acc;
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  const IO* in = static_cast<const IO*>(a.in[blockIdx.y]);
+  char* own = c.staging[t.rank];
+  const int64_t ntiles = ceilDiv(s.qv, kThreads);
+  for (int chunk = 0; chunk < t.world; ++chunk) {
+    const bool aligned = chunkAligned(in, s, chunk);
+    for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+      const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, s.qv);
+      UserRaw<IO, V> raw[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (tb.ok[u])
+          userIssue<IO, V>(raw[u], in + (int64_t)chunk * s.chunk_stride + tb.v[u] * V,
+                           aligned && validInVector(s, chunk, tb.v[u], V) == V);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (!tb.ok[u]) continue;
+        const int nvalid = (int)validInVector(s, chunk, tb.v[u], V);
+        Acc x[V];
+        userFinish<IO, V>(raw[u], in + (int64_t)chunk * s.chunk_stride + tb.v[u] * V, nvalid,
+                          aligned && nvalid == V, x);
+        applyScale(x, a.scale);
+        stStage(stageAt(own, bc.half, (int64_t)chunk * s.qv + tb.v[u]), pack<WIRE, V>(x));
+      }
+    }
+  }
+}
+template <typename IO, typename WIRE>
+__device__ __forceinline__ void phaseCopyIn(const ChannelDev& c, const OpArgs& a,
+                                            const BlockCtx& bc) {
+  constexpr int NV = sizeof(IO) / sizeof(WIRE);
+  phaseCopyInU<IO, WIRE, 4 / NV>(c, a, bc);
+}
+
+template <typename IO, typename WIRE>
+__device__ __forceinline__ void phaseCopyOut(const ChannelDev& c, const OpArgs& a,
+                                             const BlockCtx& bc) {
+  constexpr int V = kVecBytes / sizeof(WIRE);
+  constexpr int U = 4;
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  IO* out = static_cast<IO*>(a.out[blockIdx.y]);
+  char* own = c.staging[t.rank];
+  const int64_t ntiles = ceilDiv(s.qv, kThreads);
+  for (int chunk = 0; chunk < t.world; ++chunk) {
+    const bool aligned = chunkAligned(out, s, chunk);
+    for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+      const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, s.qv);
+      uint4 raw[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (tb.ok[u]) raw[u] = ldStage(stageAt(own, bc.half, (int64_t)chunk * s.qv + tb.v[u]));
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (tb.ok[u])
+          storeUserFromWire<IO, WIRE, V>(out + (int64_t)chunk * s.chunk_stride + tb.v[u] * V,
+                                         (int)validInVector(s, chunk, tb.v[u], V), aligned, raw[u]);
+    }
+  }
+}
+
+// The switch reduces this rank's chunk over all GPUs; the result is multicast
+// back into every GPU's staging, in place.
+template <typename WIRE>
+__device__ __forceinline__ void phaseNvlsReduceBroadcast(const ChannelDev& c, const OpArgs& a,
+                                                         const BlockCtx& bc) {
+  constexpr int U = 4;
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  const int64_t ntiles = ceilDiv(s.qv, kThreads);
+  for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+    const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, s.qv);
+    uint4 r[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (tb.ok[u])
+        r[u] = multimemLdReduce<WIRE>(
+            stageAt(c.mc_staging, bc.half, (int64_t)t.rank * s.qv + tb.v[u]), a.op);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (tb.ok[u])
+        multimemSt(stageAt(c.mc_staging, bc.half, (int64_t)t.rank * s.qv + tb.v[u]), r[u]);
+  }
+}
+
+// The switch reduces the whole message for this GPU, straight into the output.
+template <typename IO, typename WIRE>
+__device__ __forceinline__ void phaseNvlsReduceAll(const ChannelDev& c, const OpArgs& a,
+                                                   const BlockCtx& bc) {
+  constexpr int V = kVecBytes / sizeof(WIRE);
+  constexpr int U = 4;
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  IO* out = static_cast<IO*>(a.out[blockIdx.y]);
+  const int64_t ntiles = ceilDiv(s.qv, kThreads);
+  for (int chunk = 0; chunk < t.world; ++chunk) {
+    const bool aligned = chunkAligned(out, s, chunk);
+    for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+      const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, s.qv);
+      uint4 r[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (tb.ok[u])
+          r[u] = multimemLdReduce<WIRE>(
+              stageAt(c.mc_staging, bc.half, (int64_t)chunk * s.qv + tb.v[u]), a.op);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (tb.ok[u])
+          storeUserFromWire<IO, WIRE, V>(out + (int64_t)chunk * s.chunk_stride + tb.v[u] * V,
+                                         (int)validInVector(s, chunk, tb.v[u], V), aligned, r[u]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Kernel bodies: phase programs.  Barrier indices are fixed per collective so
+// that the three hierarchical kernels of one all_reduce share a numbering.
+//   0: after the first push / copy-in   (always all ranks)
+//   1: shard server start (rail)        2: shard server end (rail)
+//   3: gather start (group)
+// ---------------------------------------------------------------------------
+template <typename IO, typename WIRE, KernelId K>
+__device__ __forceinline__ void body(const ChannelDev& c, const OpArgs& a) {
+  const BlockCtx bc = enter(c);
+  if constexpr (K == KernelId::ONESHOT) {
+    phasePushAll<IO, WIRE>(c, a, bc);
+    if (barrier<kAll>(c, bc, 0)) phaseReduceAll<IO, WIRE>(c, a, bc);
+  } else if constexpr (K == KernelId::TWOSHOT) {
+    phasePush<IO, WIRE>(c, a, bc);
+    if (barrier<kAll>(c, bc, 0)) {
+      phaseLocalReduce<IO, WIRE>(c, a, bc);
+      if (barrier<kGroup>(c, bc, 3)) phaseGather<IO, WIRE>(c, a, bc);
+    }
+  } else if constexpr (K == KernelId::RS_INTRAGROUP) {
+    phasePush<IO, WIRE>(c, a, bc);
+    if (barrier<kAll>(c, bc, 0)) phaseLocalReduce<IO, WIRE>(c, a, bc);
+  } else if constexpr (K == KernelId::SHARD_SERVER_REDUCE) {
+    if (barrier<kRail>(c, bc, 1)) {
+      phaseServerReduce<IO, WIRE>(c, a, bc);
+      if (!(a.flags & kToUser)) barrier<kRail>(c, bc, 2);
+    }
+  } else if constexpr (K == KernelId::AG_INTRAGROUP) {
+    if (barrier<kGroup>(c, bc, 3)) phaseGather<IO, WIRE>(c, a, bc);
+  } else if constexpr (K == KernelId::DIFFUSE) {
+    phaseDiffuse<IO, WIRE>(c, a, bc);
+    barrier<kAll>(c, bc, 0);
+  } else if constexpr (K == KernelId::NVLS_TWOSHOT) {
+    phaseCopyIn<IO, WIRE>(c, a, bc);
+    if (barrier<kAll>(c, bc, 0)) {
+      phaseNvlsReduceBroadcast<WIRE>(c, a, bc);
+      if (barrier<kAll>(c, bc, 3)) phaseCopyOut<IO, WIRE>(c, a, bc);
+    }
+  } else if constexpr (K == KernelId::NVLS_ONESHOT) {
+    phaseCopyIn<IO, WIRE>(c, a, bc);
+    if (barrier<kAll>(c, bc, 0)) phaseNvlsReduceAll<IO, WIRE>(c, a, bc);
+  }
+  leave(c, a, bc);
+}
+
+// One __global__ per kernel id so that profiles show the stage by name.
+// grid.x = blocks of one rank; grid.y = 1 in a real job, = world when all ranks
+// are emulated on one GPU (then chs[] and the in/out arrays hold one entry per
+// rank).  The channel description lives in device memory: it never changes.
+#define FR_DEFINE_KERNEL(NAME, KID)                                                         \
+  template <typename IO, typename WIRE>                                                     \
+  __global__ void __launch_bounds__(kThreads, 1)                                            \
+      NAME(const ChannelDev* __restrict__ chs, const __grid_constant__ OpArgs a) {          \
+    body<IO, WIRE, KID>(chs[blockIdx.y], a);                                                \
+  }
+
+FR_DEFINE_KERNEL(oneshot_allreduce, KernelId::ONESHOT)
+FR_DEFINE_KERNEL(twoshot_allreduce, KernelId::TWOSHOT)
+FR_DEFINE_KERNEL(rs_intragroup, KernelId::RS_INTRAGROUP)
+FR_DEFINE_KERNEL(shard_server_reduce, KernelId::SHARD_SERVER_REDUCE)
+FR_DEFINE_KERNEL(ag_intragroup, KernelId::AG_INTRAGROUP)
+FR_DEFINE_KERNEL(diffuse_rail, KernelId::DIFFUSE)
+FR_DEFINE_KERNEL(nvls_allreduce, KernelId::NVLS_TWOSHOT)
+FR_DEFINE_KERNEL(nvls_oneshot_allreduce, KernelId::NVLS_ONESHOT)
+
+
+using KernelFn = void (*)(const ChannelDev*, const OpArgs);
+
+template <typename IO, typename WIRE>
+KernelFn kernelFor(KernelId id) {
+  switch (id) {
+    case KernelId::ONESHOT: return oneshot_allreduce<IO, WIRE>;
+    case KernelId::TWOSHOT: return twoshot_allreduce<IO, WIRE>;
+    case KernelId::RS_INTRAGROUP: return rs_intragroup<IO, WIRE>;
+    case KernelId::SHARD_SERVER_REDUCE: return shard_server_reduce<IO, WIRE>;
+    case KernelId::AG_INTRAGROUP: return ag_intragroup<IO, WIRE>;
+    case KernelId::DIFFUSE: return diffuse_rail<IO, WIRE>;
+    case KernelId::NVLS_TWOSHOT:
+      if constexpr (std::is_floating_point<typename Tr<WIRE>::Acc>::value && sizeof(WIRE) <= 4)
+        return nvls_allreduce<IO, WIRE>;
+      return nullptr;
+    case KernelId::NVLS_ONESHOT:
+      if constexpr (std::is_floating_point<typename Tr<WIRE>::Acc>::value && sizeof(WIRE) <= 4)
+        return nvls_oneshot_allreduce<IO, WIRE>;
+      return nullptr;
+    default: return nullptr;
+  }
+}
+
+}  // namespace impl
+}  // namespace fairring
+
+// One translation unit per (tensor dtype, wire dtype) pair instantiates the
+// kernels and exports a lookup function; they compile in parallel.
+#define FR_INSTANTIATE_COMBO(TAG, IO_T, WIRE_T)                                  \
+  namespace fairring {                                                           \
+  impl::KernelFn lookupKernel_##TAG(KernelId id) { return impl::kernelFor<IO_T, WIRE_T>(id); } \
+  }

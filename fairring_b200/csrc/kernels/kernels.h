@@ -15,9 +15,10 @@
 
 namespace fairring {
 
-// Everything one channel's kernels need to reach their peers.  Passed by
-// value (it is ~230 bytes).  A channel owns one staging slot (two halves used
-// alternately by consecutive collectives), one flag pad and one stream.
+// Everything one channel's kernels need to reach their peers.  Built once,
+// kept in device memory and passed by pointer.  A channel owns one staging
+// slot (two halves used alternately by consecutive collectives), one flag pad
+// and one stream.
 struct ChannelDev {
   char* staging[kMaxRanks];     // rank p's slot as mapped in this process
   uint32_t* flags[kMaxRanks];   // rank p's flag pad: [source rank][block]
@@ -39,8 +40,10 @@ enum OpFlags : uint32_t {
 };
 
 struct OpArgs {
-  const void* in;   // slice base in the user's input
-  void* out;        // slice base in the user's output (may alias `in`)
+  // Slice base in the user's input / output (may alias).  Entry 0 in a real
+  // job; one entry per rank when all ranks are emulated on one GPU.
+  const void* in[kMaxRanks];
+  void* out[kMaxRanks];
   Seg seg;
   float scale;      // multiplied in while the data is first read (floating types)
   int32_t op;       // RedOp
@@ -71,14 +74,16 @@ bool nvlsSupported(DType wire, RedOp op);
 
 constexpr int kThreads = 512;
 
-// One rank per process: the usual launch.
-cudaError_t launchCollective(KernelId id, const ChannelDev& ch, const OpArgs& args,
+// One rank per process: the usual launch.  `ch_dev` points to the channel's
+// description in device memory; args.in[0] / args.out[0] are used.
+cudaError_t launchCollective(KernelId id, const ChannelDev* ch_dev, const OpArgs& args,
                              int blocks, cudaStream_t stream);
 
 // All `world` ranks inside one cooperative launch on one GPU (grid.y = rank):
 // how the multi-rank logic is exercised when fewer GPUs than ranks are at hand.
-// `chs` and `args` are device arrays of `world` entries.
-cudaError_t launchEmulated(KernelId id, const ChannelDev* chs, const OpArgs* args,
+// `chs_dev` is a device array of `world` channel descriptions; args.in[r] /
+// args.out[r] are rank r's tensors.
+cudaError_t launchEmulated(KernelId id, const ChannelDev* chs_dev, const OpArgs& args,
                            int world, int blocks, cudaStream_t stream);
 
 // Number of kernels this library has launched in this process.
