@@ -29,6 +29,8 @@ FAIRRING_NVLS                  auto | on | off   (NVSwitch multicast kernels)
 FAIRRING_NVLS_MIN              smallest message (bytes) for the NVLS two-shot kernel
 FAIRRING_NVLS_ONESHOT_MAX      largest message (bytes) for the NVLS one-shot kernel
 FAIRRING_TRANSPORT             auto | vmm | ipc  (how peer memory is shared)
+FAIRRING_DIRECT                auto | nvls | p2p | off  (in-place kernels for tensors from
+                               ``symmetric_empty``: no staging copies)
 FAIRRING_DEVICE_TIMEOUT_MS     limit of one device-side wait on a peer (default 30000)
 FAIRRING_COMMAND_THREAD        1: enqueue kernels from a dedicated thread
 FAIRRING_BLOCKING_WAIT         1: Work.wait() blocks the host and reports kernel failures
@@ -108,6 +110,7 @@ def options_from_env(timeout: timedelta | None = None) -> "_C.Options":
     opts.device_timeout_ms = _env_int("FAIRRING_DEVICE_TIMEOUT_MS", opts.device_timeout_ms)
     opts.nvls = os.environ.get("FAIRRING_NVLS", "auto").lower()
     opts.transport = os.environ.get("FAIRRING_TRANSPORT", "auto").lower()
+    opts.direct = os.environ.get("FAIRRING_DIRECT", "auto").lower()
     opts.command_thread = os.environ.get("FAIRRING_COMMAND_THREAD", "0") == "1"
     opts.blocking_wait = os.environ.get("FAIRRING_BLOCKING_WAIT", "0") == "1"
     opts.boot_id_override = os.environ.get("FAIRRING_BOOT_ID", "")

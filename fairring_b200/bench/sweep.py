@@ -41,6 +41,8 @@ def main(argv=None) -> int:
     ap.add_argument("--backends", default="fairring,nccl")
     ap.add_argument("--arena-bytes", type=int, default=1 << 30)
     ap.add_argument("--check", action="store_true", help="verify one result per size")
+    ap.add_argument("--symmetric", action="store_true",
+                    help="put the fairring arena in symmetric memory (in-place kernels, no staging)")
     ap.add_argument("--json", default="", help="also write the rows to this file")
     args = ap.parse_args(argv)
 
@@ -63,15 +65,21 @@ def main(argv=None) -> int:
         es = torch.empty((), dtype=dtype).element_size()
         gen = torch.Generator(device=dev).manual_seed(rank)
         arena = torch.randn(arena_bytes // es, generator=gen, device=dev, dtype=dtype)
+        sym_arena = None
+        if args.symmetric and "fairring" in groups:
+            sym_arena = fairring_b200.get_backend(device="cuda").symmetric_empty(arena.numel(), dtype)
+            sym_arena.copy_(arena)
         size = args.min_bytes
         while size <= args.max_bytes:
             n = size // es
             slots = max(1, (arena_bytes // es) // n)
             iters = 200 if size <= (1 << 20) else (40 if size <= (64 << 20) else 10)
             for bname, group in groups.items():
-                def call(i, n=n, slots=slots, group=group):
+                buf = sym_arena if (bname == "fairring" and sym_arena is not None) else arena
+
+                def call(i, n=n, slots=slots, group=group, buf=buf):
                     j = i % slots
-                    dist.all_reduce(arena[j * n:(j + 1) * n], group=group)
+                    dist.all_reduce(buf[j * n:(j + 1) * n], group=group)
 
                 for i in range(5):
                     call(i)
@@ -83,11 +91,12 @@ def main(argv=None) -> int:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
                 us = float(t.item())
                 busbw = 2 * (world - 1) / world * size / (us * 1e-6) / 1e9 if world > 1 else 0.0
-                rows.append({"backend": bname, "dtype": dname, "bytes": size, "us": round(us, 2),
+                rows.append({"backend": bname + ("(symmetric)" if buf is sym_arena and sym_arena is not None else ""),
+                             "dtype": dname, "bytes": size, "us": round(us, 2),
                              "algbw_gbs": round(size / (us * 1e-6) / 1e9, 2),
                              "busbw_gbs": round(busbw, 2), "world": world})
                 # values drift as the arena is summed over and over: renormalise
-                arena.mul_(0.0).add_(torch.randn(arena.shape, generator=gen, device=dev, dtype=dtype))
+                buf.copy_(torch.randn(arena.shape, generator=gen, device=dev, dtype=dtype))
             if args.check:
                 x = torch.full((n,), float(rank + 1), device=dev, dtype=dtype)
                 dist.all_reduce(x)
@@ -102,7 +111,7 @@ def main(argv=None) -> int:
         print(f"{'dtype':6} {'bytes':>12} " + " ".join(f"{b + ' us':>14} {b + ' busGB/s':>16}" for b in groups))
         by = {}
         for r in rows:
-            by.setdefault((r["dtype"], r["bytes"]), {})[r["backend"]] = r
+            by.setdefault((r["dtype"], r["bytes"]), {})[r["backend"].split("(")[0]] = r
         for (dname, size), d in by.items():
             print(f"{dname:6} {size:12d} " + " ".join(
                 f"{d[b]['us']:14.2f} {d[b]['busbw_gbs']:16.2f}" for b in groups))

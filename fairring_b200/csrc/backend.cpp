@@ -3,6 +3,7 @@
 
 #include <ATen/ATen.h>
 #include <c10/cuda/CUDACachingAllocator.h>
+#include <c10/cuda/CUDAFunctions.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/csrc/distributed/c10d/PrefixStore.hpp>
@@ -205,6 +206,7 @@ std::shared_ptr<Engine> BackendFairring::ensureEngine(int device) {
   cfg.command_thread = options_->command_thread;
   cfg.transport = parseTransport(options_->transport);
   cfg.nvls = parseNvls(options_->nvls);
+  cfg.direct = options_->direct;
   cfg.bootstrap_timeout = options_->timeout;
   c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
   engine_ = std::make_shared<Engine>(std::make_shared<StoreAdapter>(store_, "fairring/gpu/"),
@@ -717,6 +719,28 @@ void BackendFairring::checkHealth() {
 void BackendFairring::reset() {
   std::lock_guard<std::mutex> lk(mu_);
   if (engine_) engine_->reset();
+}
+
+at::Tensor BackendFairring::symmetricEmpty(int64_t numel, at::ScalarType dtype) {
+  TORCH_CHECK(numel > 0, "fairring: symmetric_empty needs a positive size");
+  std::lock_guard<std::mutex> lk(mu_);
+  const Deployment& dep = ensureDeployment();
+  TORCH_CHECK(dep.single_host && dep.topo.world <= kMaxRanks,
+              "fairring: symmetric memory needs all ranks on one NVSwitch host");
+  const int device = engine_ ? engine_device_ : (int)c10::cuda::current_device();
+  auto engine = ensureEngine(device);
+  const size_t bytes = (size_t)numel * c10::elementSize(dtype);
+  void* p = nullptr;
+  try {
+    p = engine->allocSymmetric(bytes);
+  } catch (const Error& e) {
+    TORCH_CHECK(false, e.what());
+  }
+  // The memory belongs to the engine (it is unmapped when the process group
+  // goes away); the tensor only borrows it.
+  auto keep = engine;
+  return at::from_blob(p, {numel}, [keep](void*) {},
+                       at::TensorOptions().dtype(dtype).device(at::kCUDA, (c10::DeviceIndex)device));
 }
 
 void BackendFairring::skipCpuSignals(int n) {

@@ -51,6 +51,7 @@ struct OptionsFairring : c10d::Backend::Options {
   int64_t device_timeout_ms = 30000;
   std::string nvls = "auto";       // auto | on | off
   std::string transport = "auto";  // auto | vmm | ipc
+  std::string direct = "auto";     // auto | p2p | nvls | off: in-place path for symmetric tensors
   bool command_thread = false;
   bool blocking_wait = false;
   std::string boot_id_override;    // tests: pretend to be on another host
@@ -161,6 +162,9 @@ class BackendFairring : public c10d::Backend {
   void checkHealth();
   void reset();
   void skipCpuSignals(int n);
+  // Collective: a 1-D tensor in symmetric memory of the current CUDA device;
+  // all_reduce on (slices of) it runs in place without staging copies.
+  at::Tensor symmetricEmpty(int64_t numel, at::ScalarType dtype);
   std::map<std::string, int64_t> deployment();
 
  private:

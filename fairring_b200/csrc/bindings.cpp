@@ -69,6 +69,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("device_timeout_ms", &OptionsFairring::device_timeout_ms)
       .def_readwrite("nvls", &OptionsFairring::nvls)
       .def_readwrite("transport", &OptionsFairring::transport)
+      .def_readwrite("direct", &OptionsFairring::direct)
       .def_readwrite("command_thread", &OptionsFairring::command_thread)
       .def_readwrite("blocking_wait", &OptionsFairring::blocking_wait)
       .def_readwrite("boot_id_override", &OptionsFairring::boot_id_override)
@@ -112,6 +113,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("reset", &BackendFairring::reset, py::call_guard<py::gil_scoped_release>())
       .def("abort", &BackendFairring::abort, py::call_guard<py::gil_scoped_release>())
       .def("shutdown", &BackendFairring::shutdown, py::call_guard<py::gil_scoped_release>())
+      .def("symmetric_empty", &BackendFairring::symmetricEmpty, py::arg("numel"), py::arg("dtype"),
+           py::call_guard<py::gil_scoped_release>())
       .def("skip_cpu_signals", &BackendFairring::skipCpuSignals,
            py::call_guard<py::gil_scoped_release>());
 

@@ -132,7 +132,27 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
 
   for (int64_t rep = 0; rep < repeats; ++rep) {
     if (is_ar) {
-      if (algo == "oneshot") {
+      if (algo == "direct") {
+        // In place on the ranks' own tensors: what the engine does for tensors
+        // in symmetric memory.
+        TORCH_CHECK(io == wire && (n_in * wes) % kVecBytes == 0, "direct needs whole vectors");
+        OpArgs a;
+        std::memset(&a, 0, sizeof(a));
+        for (int r = 0; r < W; ++r) {
+          TORCH_CHECK((reinterpret_cast<uintptr_t>(inputs[r].data_ptr()) & 15u) == 0, "misaligned");
+          a.peer[r] = inputs[r].data_ptr();
+          a.in[r] = a.out[r] = inputs[r].data_ptr();
+        }
+        a.seg = allreduceSeg(n_in, wes, W);
+        a.scale = (float)scale;
+        a.op = (int32_t)rop;
+        a.io_dtype = a.wire_dtype = (int32_t)io;
+        a.flags = kAdvanceSeq;
+        cudaError_t e = launchEmulated(KernelId::P2P_DIRECT,
+                                       static_cast<const ChannelDev*>(chs_dev.data_ptr()), a, W,
+                                       (int)blocks, stream);
+        TORCH_CHECK(e == cudaSuccess, "emulated direct launch failed: ", cudaGetErrorString(e));
+      } else if (algo == "oneshot") {
         const Seg s = allreduceSeg(n_in, wes, W);
         TORCH_CHECK((int64_t)W * W * s.qv * kVecBytes <= half_bytes, "message too large for one-shot");
         launchAll(KernelId::ONESHOT, s, 0, 0, kAdvanceSeq);

@@ -139,6 +139,7 @@ Engine::~Engine() {
   cudaSetDevice(device_);
   cudaDeviceSynchronize();
   try {
+    for (auto& r : user_regions_) alloc_->release(r);
     alloc_->release(region_);
   } catch (const std::exception&) {
   }
@@ -221,6 +222,67 @@ void Engine::reset() {
   std::memset(status_host_, 0, ((size_t)plan_.channels * kStatusWords + 16) * sizeof(uint32_t));
   poisoned_ = false;
   store_->barrier(pfx + "/clean", topo_.world, cfg_.bootstrap_timeout);
+}
+
+void* Engine::allocSymmetric(size_t bytes) {
+  std::lock_guard<std::mutex> lk(mu_);
+  FR_CUDA(cudaSetDevice(device_));
+  user_regions_.push_back(alloc_->allocate(bytes, /*want_multicast=*/true));
+  return user_regions_.back().ptrs[topo_.rank];
+}
+
+bool Engine::findSymmetric(const void* p, size_t bytes, const SymmRegion** reg, size_t* off) const {
+  const char* q = static_cast<const char*>(p);
+  for (const auto& r : user_regions_) {
+    const char* base = static_cast<const char*>(r.ptrs[topo_.rank]);
+    if (q >= base && q + bytes <= base + r.bytes) {
+      *reg = &r;
+      *off = (size_t)(q - base);
+      return true;
+    }
+  }
+  return false;
+}
+
+// All-reduce in place on symmetric memory.  Returns false if the tensor does
+// not qualify (then the staged path is taken).
+bool Engine::runDirect(const CollectiveDesc& d, const std::function<Channel&()>& take) {
+  if (cfg_.direct == "off" || d.kind != CollKind::ALLREDUCE || topo_.M != 1 || topo_.world < 2)
+    return false;
+  if (d.in != d.out || d.io != d.wire) return false;
+  const int es = dtypeSize(d.io);
+  const size_t bytes = (size_t)d.numel * es;
+  if ((reinterpret_cast<uintptr_t>(d.out) & 15u) != 0 || bytes % kVecBytes != 0) return false;
+  if ((int64_t)bytes <= cfg_.oneshot_max_bytes) return false;  // one barrier beats two
+  const SymmRegion* reg = nullptr;
+  size_t off = 0;
+  if (!findSymmetric(d.out, bytes, &reg, &off)) return false;
+  const bool nvls = reg->mc_ptr != nullptr && nvlsSupported(d.wire, d.op) && cfg_.direct != "p2p";
+  if (cfg_.direct == "nvls" && !nvls) return false;
+  const int W = topo_.world;
+  const int64_t V = kVecBytes / es;
+  int64_t nslices = (int64_t)bytes / cfg_.direct_min_slice_bytes;
+  if (nslices > (int64_t)channels_.size()) nslices = (int64_t)channels_.size();
+  if (nslices < 1) nslices = 1;
+  const int64_t slice_elems = roundUp(ceilDiv(d.numel, nslices), V * W);
+  for (int64_t start = 0; start < d.numel; start += slice_elems) {
+    const int64_t n = std::min(slice_elems, d.numel - start);
+    OpArgs a{};
+    a.seg = allreduceSeg(n, es, W);
+    a.scale = d.scale;
+    a.op = (int32_t)d.op;
+    a.io_dtype = (int32_t)d.io;
+    a.wire_dtype = (int32_t)d.wire;
+    a.flags = kAdvanceSeq;
+    const size_t o = off + (size_t)start * es;
+    for (int r = 0; r < W; ++r) a.peer[r] = static_cast<char*>(reg->ptrs[r]) + o;
+    a.mc = nvls ? static_cast<char*>(reg->mc_ptr) + o : nullptr;
+    a.in[0] = a.out[0] = a.peer[topo_.rank];
+    launch(take(), nvls ? KernelId::NVLS_DIRECT : KernelId::P2P_DIRECT, a);
+    ++stats_.slices;
+  }
+  stats_.wire_bytes += bytes;
+  return true;
 }
 
 EngineStats Engine::stats() const { return stats_; }
@@ -314,7 +376,7 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after) {
   const int ies = dtypeSize(d.io), wes = dtypeSize(d.wire);
   const int64_t V = kVecBytes / wes;
   std::vector<int> used;
-  auto take = [&]() -> Channel& {
+  std::function<Channel&()> take = [&]() -> Channel& {
     const int c = (int)(next_channel_++ % channels_.size());
     if (std::find(used.begin(), used.end(), c) == used.end()) {
       FR_CUDA(cudaStreamWaitEvent(channels_[c].stream, after, 0));
@@ -326,7 +388,9 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after) {
   char* out = static_cast<char*>(d.out);
   ++stats_.collectives;
 
-  if (d.kind == CollKind::ALLREDUCE) {
+  if (runDirect(d, take)) {
+    // nothing else to do
+  } else if (d.kind == CollKind::ALLREDUCE) {
     const int64_t bytes = d.numel * wes;
     const Algo whole = chooseAllreduce(bytes, d.wire, d.op);
     if (whole == Algo::ONESHOT ||
@@ -334,7 +398,12 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after) {
       runAllreduceSlice(take(), d, in, out, d.numel, whole);
       ++stats_.slices;
     } else {
-      const SlicePlan sp = planSlices(d.numel, wes, W, plan_.max_slice_bytes);
+      // A big message is spread over all channels (more blocks in flight),
+      // down to direct_min_slice_bytes per slice.
+      int64_t cap = std::max<int64_t>(cfg_.direct_min_slice_bytes,
+                                      ceilDiv(bytes, (int64_t)channels_.size()));
+      if (cap > plan_.max_slice_bytes) cap = plan_.max_slice_bytes;
+      const SlicePlan sp = planSlices(d.numel, wes, W, cap);
       for (int64_t k = 0; k < sp.num_slices; ++k) {
         const int64_t off = k * sp.slice_elems;
         const int64_t n = std::min(sp.slice_elems, d.numel - off);

@@ -48,6 +48,10 @@ struct EngineConfig {
   bool command_thread = false;
   SymmTransport transport = SymmTransport::AUTO;
   NvlsMode nvls = NvlsMode::AUTO;
+  // Tensors allocated with allocSymmetric() are all-reduced in place, without
+  // staging: "auto" (NVLS when possible, else peer loads), "p2p", "nvls", "off".
+  std::string direct = "auto";
+  int64_t direct_min_slice_bytes = 2ll << 20;  // a message is split over channels down to this
   std::chrono::milliseconds bootstrap_timeout{120000};
 };
 
@@ -108,6 +112,11 @@ class Engine {
   // Collective: after a failure, bring flags and sequence numbers back to zero.
   void reset();
 
+  // Collective: symmetric device memory (peer-mapped everywhere, multicast
+  // alias when available) that lives as long as the engine.  all_reduce on a
+  // tensor inside it runs in place with no staging copies.
+  void* allocSymmetric(size_t bytes);
+
   const Topo& topo() const { return topo_; }
   const MemoryPlan& plan() const { return plan_; }
   const EngineConfig& config() const { return cfg_; }
@@ -127,6 +136,8 @@ class Engine {
   void runAllreduceSlice(Channel& ch, const CollectiveDesc& d, const void* in, void* out,
                          int64_t n, Algo algo);
   cudaEvent_t nextEvent();
+  bool findSymmetric(const void* p, size_t bytes, const SymmRegion** reg, size_t* off) const;
+  bool runDirect(const CollectiveDesc& d, const std::function<Channel&()>& take);
 
   std::shared_ptr<KvStore> store_;
   Topo topo_;
@@ -135,6 +146,7 @@ class Engine {
   MemoryPlan plan_;
   std::unique_ptr<SymmAllocator> alloc_;
   SymmRegion region_;
+  std::vector<SymmRegion> user_regions_;
   size_t flags_bytes_ = 0;
   uint32_t* seq_dev_ = nullptr;
   uint32_t* status_host_ = nullptr;  // pinned + mapped: [channels][kStatusWords], then abort word

@@ -51,6 +51,8 @@ const char* kernelName(KernelId id) {
     case KernelId::DIFFUSE: return "diffuse_rail";
     case KernelId::NVLS_TWOSHOT: return "nvls_allreduce";
     case KernelId::NVLS_ONESHOT: return "nvls_oneshot_allreduce";
+    case KernelId::P2P_DIRECT: return "direct_allreduce";
+    case KernelId::NVLS_DIRECT: return "nvls_direct_allreduce";
     default: return "?";
   }
 }
@@ -71,9 +73,11 @@ cudaError_t launchImpl(KernelId id, const ChannelDev* chs, const OpArgs& args, i
   if (blocks < 1 || blocks > kMaxBlocks) return cudaErrorInvalidValue;
   KernelFn fn = lookup((DType)args.io_dtype, (DType)args.wire_dtype, id);
   if (fn == nullptr) return cudaErrorInvalidDeviceFunction;
-  if ((id == KernelId::NVLS_TWOSHOT || id == KernelId::NVLS_ONESHOT) &&
+  if ((id == KernelId::NVLS_TWOSHOT || id == KernelId::NVLS_ONESHOT ||
+       id == KernelId::NVLS_DIRECT) &&
       !nvlsSupported((DType)args.wire_dtype, (RedOp)args.op))
     return cudaErrorInvalidValue;
+  if (id == KernelId::NVLS_DIRECT && args.mc == nullptr) return cudaErrorInvalidValue;
   cudaError_t e;
   if (cooperative) {
     // All blocks of all emulated ranks wait on one another: they must be
@@ -98,7 +102,7 @@ cudaError_t launchCollective(KernelId id, const ChannelDev* ch_dev, const OpArgs
 cudaError_t launchEmulated(KernelId id, const ChannelDev* chs_dev, const OpArgs& args, int world,
                            int blocks, cudaStream_t stream) {
   if (world < 1 || world > kMaxRanks) return cudaErrorInvalidValue;
-  if (id == KernelId::NVLS_TWOSHOT || id == KernelId::NVLS_ONESHOT)
+  if (id == KernelId::NVLS_TWOSHOT || id == KernelId::NVLS_ONESHOT || id == KernelId::NVLS_DIRECT)
     return cudaErrorInvalidValue;  // multicast needs one GPU per rank
   return launchImpl(id, chs_dev, args, world, blocks, true, stream);
 }

@@ -688,6 +688,103 @@ __device__ __forceinline__ void phaseNvlsReduceAll(const ChannelDev& c, const Op
 }
 
 // ---------------------------------------------------------------------------
+// Direct phases: the tensor itself is symmetric memory, nothing is staged.
+// The slice is W chunks of qv vectors (whole vectors only: the engine takes
+// this path for 16-byte aligned slices whose length is a multiple of 16 bytes).
+// Rank r owns chunk r: it reads chunk r of every rank's tensor, reduces, scales
+// and writes the result into chunk r of every rank's tensor.  Vector v of chunk
+// r is read and then written by the same thread, and no other rank touches
+// chunk r, so the update is safe in place.
+// ---------------------------------------------------------------------------
+template <typename WIRE, int U, int KP>
+__device__ __forceinline__ void phaseDirectPeerU(const ChannelDev& c, const OpArgs& a,
+                                                 const BlockCtx& bc) {
+  constexpr int V = kVecBytes / sizeof(WIRE);
+  using Acc = typename Tr<WIRE>::Acc;
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  const int W = t.world;
+  const int64_t nvec = ceilDiv(s.limit, V);
+  const int64_t base = (int64_t)t.rank * s.qv;
+  int64_t mine = nvec - base;
+  if (mine > s.qv) mine = s.qv;
+  if (mine < 0) mine = 0;
+  const int64_t ntiles = ceilDiv(mine, kThreads);
+  for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+    const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, mine);
+    uint4 raw[U][KP];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int k = 0; k < KP; ++k)
+        if (k < W && tb.ok[u])
+          raw[u][k] = ldStage(static_cast<char*>(a.peer[k]) + (base + tb.v[u]) * kVecBytes);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!tb.ok[u]) continue;
+      Acc acc[V];
+      unpack<WIRE, V>(raw[u][0], acc);
+#pragma unroll
+      for (int k = 1; k < KP; ++k) {
+        if (k < W) {
+          Acc x[V];
+          unpack<WIRE, V>(raw[u][k], x);
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc[i] = combine(acc[i], x[i], a.op);
+        }
+      }
+      applyScale(acc, a.scale);
+      const uint4 r = pack<WIRE, V>(acc);
+#pragma unroll
+      for (int k = 0; k < KP; ++k)
+        if (k < W)
+          stStage(static_cast<char*>(a.peer[(t.rank + k) % W]) + (base + tb.v[u]) * kVecBytes, r);
+    }
+  }
+}
+template <typename WIRE>
+__device__ __forceinline__ void phaseDirectPeer(const ChannelDev& c, const OpArgs& a,
+                                                const BlockCtx& bc) {
+  FR_WITH_UNROLL(c.topo.world, 1, phaseDirectPeerU<WIRE, U, KP>(c, a, bc));
+}
+
+template <typename WIRE>
+__device__ __forceinline__ void phaseDirectNvls(const ChannelDev& c, const OpArgs& a,
+                                                const BlockCtx& bc) {
+  constexpr int V = kVecBytes / sizeof(WIRE);
+  constexpr int U = 4;
+  using Acc = typename Tr<WIRE>::Acc;
+  const Topo& t = c.topo;
+  const Seg& s = a.seg;
+  const int64_t nvec = ceilDiv(s.limit, V);
+  const int64_t base = (int64_t)t.rank * s.qv;
+  int64_t mine = nvec - base;
+  if (mine > s.qv) mine = s.qv;
+  if (mine < 0) mine = 0;
+  char* mc = static_cast<char*>(a.mc);
+  const int64_t ntiles = ceilDiv(mine, kThreads);
+  for (int64_t tile0 = bc.b; tile0 < ntiles; tile0 += (int64_t)bc.G * U) {
+    const Batch<U> tb = batchAt<U>(tile0, bc, ntiles, mine);
+    uint4 r[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (tb.ok[u]) r[u] = multimemLdReduce<WIRE>(mc + (base + tb.v[u]) * kVecBytes, a.op);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!tb.ok[u]) continue;
+      if (a.scale != 1.0f) {
+        Acc x[V];
+        unpack<WIRE, V>(r[u], x);
+        applyScale(x, a.scale);
+        r[u] = pack<WIRE, V>(x);
+      }
+      multimemSt(mc + (base + tb.v[u]) * kVecBytes, r[u]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Kernel bodies: phase programs.  Barrier indices are fixed per collective so
 // that the three hierarchical kernels of one all_reduce share a numbering.
 //   0: after the first push / copy-in   (always all ranks)
@@ -728,6 +825,19 @@ __device__ __forceinline__ void body(const ChannelDev& c, const OpArgs& a) {
   } else if constexpr (K == KernelId::NVLS_ONESHOT) {
     phaseCopyIn<IO, WIRE>(c, a, bc);
     if (barrier<kAll>(c, bc, 0)) phaseNvlsReduceAll<IO, WIRE>(c, a, bc);
+  } else if constexpr (K == KernelId::P2P_DIRECT) {
+    // Barrier 0: every rank's tensor is ready (a rank signals from this kernel,
+    // which its stream runs after the producer).  Barrier 3: all results have
+    // landed everywhere, the tensor may be used again.
+    if (barrier<kAll>(c, bc, 0)) {
+      phaseDirectPeer<WIRE>(c, a, bc);
+      barrier<kAll>(c, bc, 3);
+    }
+  } else if constexpr (K == KernelId::NVLS_DIRECT) {
+    if (barrier<kAll>(c, bc, 0)) {
+      phaseDirectNvls<WIRE>(c, a, bc);
+      barrier<kAll>(c, bc, 3);
+    }
   }
   leave(c, a, bc);
 }
@@ -751,6 +861,8 @@ FR_DEFINE_KERNEL(ag_intragroup, KernelId::AG_INTRAGROUP)
 FR_DEFINE_KERNEL(diffuse_rail, KernelId::DIFFUSE)
 FR_DEFINE_KERNEL(nvls_allreduce, KernelId::NVLS_TWOSHOT)
 FR_DEFINE_KERNEL(nvls_oneshot_allreduce, KernelId::NVLS_ONESHOT)
+FR_DEFINE_KERNEL(direct_allreduce, KernelId::P2P_DIRECT)
+FR_DEFINE_KERNEL(nvls_direct_allreduce, KernelId::NVLS_DIRECT)
 
 
 using KernelFn = void (*)(const ChannelDev*, const OpArgs);
@@ -771,6 +883,14 @@ KernelFn kernelFor(KernelId id) {
     case KernelId::NVLS_ONESHOT:
       if constexpr (std::is_floating_point<typename Tr<WIRE>::Acc>::value && sizeof(WIRE) <= 4)
         return nvls_oneshot_allreduce<IO, WIRE>;
+      return nullptr;
+    case KernelId::P2P_DIRECT:
+      if constexpr (std::is_same<IO, WIRE>::value) return direct_allreduce<IO, WIRE>;
+      return nullptr;
+    case KernelId::NVLS_DIRECT:
+      if constexpr (std::is_same<IO, WIRE>::value &&
+                    std::is_floating_point<typename Tr<WIRE>::Acc>::value && sizeof(WIRE) <= 4)
+        return nvls_direct_allreduce<IO, WIRE>;
       return nullptr;
     default: return nullptr;
   }

@@ -44,6 +44,11 @@ struct OpArgs {
   // job; one entry per rank when all ranks are emulated on one GPU.
   const void* in[kMaxRanks];
   void* out[kMaxRanks];
+  // Direct (zero-copy) kernels only: the tensor lives in symmetric memory, so
+  // every rank's copy of it is addressable.  peer[p] is rank p's copy of the
+  // slice as mapped here, mc its multicast alias (or null).
+  void* peer[kMaxRanks];
+  void* mc;
   Seg seg;
   float scale;      // multiplied in while the data is first read (floating types)
   int32_t op;       // RedOp
@@ -61,6 +66,8 @@ enum class KernelId : int32_t {
   DIFFUSE,              // all_gather stage 1: own chunk -> self slot of every rail peer
   NVLS_TWOSHOT,         // multimem.ld_reduce own chunk, multimem.st it to all
   NVLS_ONESHOT,         // multimem.ld_reduce the whole message
+  P2P_DIRECT,           // in place on symmetric memory: pull + reduce own chunk, push it to all
+  NVLS_DIRECT,          // in place on symmetric memory: multimem.ld_reduce + multimem.st
   kCount
 };
 

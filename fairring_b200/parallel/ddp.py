@@ -19,9 +19,7 @@ The reference has no training code; what it serves is DDP's bucketed gradient
 all-reduce overlapped with backward (README.md:104-110).
 """
 
-from __future__ import annotations
-
-from typing import Iterable
+from typing import Iterable, Optional
 
 import torch
 import torch.distributed as dist
@@ -33,7 +31,7 @@ from .. import get_backend
 class FusedHookState:
     """State for :func:`fused_allreduce_hook`."""
 
-    def __init__(self, process_group=None, wire_dtype: torch.dtype | None = None):
+    def __init__(self, process_group=None, wire_dtype: Optional[torch.dtype] = None):
         self.process_group = process_group if process_group is not None else dist.group.WORLD
         self.backend = get_backend(self.process_group, "cuda")
         self.world = dist.get_world_size(self.process_group)
@@ -60,7 +58,8 @@ class FlatDataParallel(nn.Module):
     """
 
     def __init__(self, module: nn.Module, process_group=None, bucket_cap_mb: float = 25.0,
-                 wire_dtype: torch.dtype | None = None, broadcast_parameters: bool = True):
+                 wire_dtype: Optional[torch.dtype] = None, broadcast_parameters: bool = True,
+                 symmetric_grads: bool = True):
         super().__init__()
         self.module = module
         self.process_group = process_group if process_group is not None else dist.group.WORLD
@@ -87,7 +86,20 @@ class FlatDataParallel(nn.Module):
             offsets.append(total)
             total += (p.numel() + align - 1) // align * align
         self.flat_param = torch.zeros(total, device=dev, dtype=torch.float32)
-        self.flat_grad = torch.zeros(total, device=dev, dtype=torch.float32)
+        # Gradients live in symmetric memory when the backend offers it: every
+        # rank's buffer is peer-mapped (and multicast-mapped) everywhere, so a
+        # bucket is all-reduced in place by the switch, with no staging copies.
+        self.symmetric = False
+        if symmetric_grads and self.world > 1 and wire_dtype is None:
+            try:
+                with torch.cuda.device(dev):
+                    self.flat_grad = self.backend.symmetric_empty(total, torch.float32)
+                self.flat_grad.zero_()
+                self.symmetric = True
+            except RuntimeError:
+                self.symmetric = False
+        if not self.symmetric:
+            self.flat_grad = torch.zeros(total, device=dev, dtype=torch.float32)
         self._params = order
         self._offsets = offsets
         for p, off in zip(order, offsets):
@@ -97,9 +109,9 @@ class FlatDataParallel(nn.Module):
             p.grad = None
 
         cap = int(bucket_cap_mb * 1024 * 1024) // 4
-        self._bucket_of: dict[int, int] = {}
-        self._buckets: list[tuple[int, int]] = []  # [start, end) in elements
-        self._bucket_size: list[int] = []
+        self._bucket_of = {}
+        self._buckets = []  # [start, end) in elements
+        self._bucket_size = []
         start, count = 0, 0
         for i, (p, off) in enumerate(zip(order, offsets)):
             end = offsets[i + 1] if i + 1 < len(order) else total
@@ -111,7 +123,7 @@ class FlatDataParallel(nn.Module):
                 start, count = end, 0
         self._pending = list(self._bucket_size)
         self._next_to_launch = 0
-        self._works: list = []
+        self._works = []
         self._callback_queued = False
         self._accumulate = False
         self.require_backward_grad_sync = True

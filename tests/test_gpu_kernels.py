@@ -121,6 +121,31 @@ def test_allreduce_fused_scale_and_wire_cast(C, wire):
             torch.testing.assert_close(outs[r].double(), expect, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_allreduce_direct_in_place(C, world):
+    """The zero-copy kernel: every rank reads its chunk from all ranks' tensors
+    and writes the result back into all of them, no staging."""
+    _need_gpu()
+    for dtype in (torch.float32, torch.bfloat16, torch.int32):
+        for n in (64, 4096, 1_000_000):
+            ins = _make(world, n, dtype, seed=n + world)
+            expect = _ref(ins, "sum")
+            work = [t.clone() for t in ins]
+            outs, status = C.emulated_collective("allreduce", work, world, algo="direct", blocks=4,
+                                                 half_bytes=1 << 16, repeats=1)
+            torch.cuda.synchronize()
+            _check_status(status)
+            for r in range(world):
+                torch.testing.assert_close(outs[r].double(), expect, **_tol(dtype, world))
+                assert torch.equal(outs[r], outs[0])
+    ins = _make(world, 8192, torch.float32, seed=1)
+    outs, status = C.emulated_collective("allreduce", [t.clone() for t in ins], world, algo="direct",
+                                         scale=0.5, op="max", blocks=2, half_bytes=1 << 16)
+    torch.cuda.synchronize()
+    _check_status(status)
+    torch.testing.assert_close(outs[0].double(), _ref(ins, "max") * 0.5, rtol=1e-6, atol=1e-6)
+
+
 def test_allreduce_misaligned_tensor(C):
     """Tensors that do not start on a 16-byte boundary take the element-wise path."""
     _need_gpu()

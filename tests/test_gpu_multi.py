@@ -74,6 +74,19 @@ def _suite(rank, world, check_ddp):
                           for r in range(world)]).sum(0)
     torch.testing.assert_close(g.double().cpu(), expect, rtol=2e-2, atol=2e-2)
 
+    # tensors in symmetric memory are reduced in place, without staging
+    sym = be.symmetric_empty(6_000_000, torch.float32)
+    for lo, hi in ((0, 6_000_000), (1024, 4_001_024), (64, 128)):
+        sym.copy_(seeded(6_000_000, torch.float32, rank, 5).to(dev))
+        dist.all_reduce(sym[lo:hi])
+        expect = torch.stack([seeded(6_000_000, torch.float32, r, 5).double() for r in range(world)]).sum(0)
+        mine = seeded(6_000_000, torch.float32, rank, 5).double()
+        mine[lo:hi] = expect[lo:hi]
+        torch.testing.assert_close(sym.double().cpu(), mine, rtol=1e-4, atol=1e-4)
+    be.allreduce_fused(sym, 1.0 / world, None, "sum").wait()
+    torch.cuda.synchronize()
+    report["direct_launches"] = be.stats()["launch_direct_allreduce"] + be.stats()["launch_nvls_direct_allreduce"]
+
     # reduce_scatter / all_gather (tensor and list forms)
     n = 70_001
     inp = torch.arange(world * n, dtype=torch.float32, device=dev) * (rank + 1)
@@ -173,6 +186,8 @@ def test_backend_on_gpus(name):
     res = run_ranks(_suite, world, env=env, args=(name == "auto",), timeout=240)
     stats = res[0]["stats"]
     assert stats["gpu_collectives"] > 50
+    if "FAIRRING_GPUS_PER_MACHINE" not in env:
+        assert res[0]["direct_launches"] > 0
     if name == "twoshot_no_nvls":
         assert stats["nvls"] == 0 and stats["launch_twoshot_allreduce"] > 0
     if name in ("nvls", "nvls_oneshot") and stats["nvls"] == 1:
