@@ -38,7 +38,9 @@ class FusedHookState:
         self.wire_dtype = wire_dtype
 
 
-def fused_allreduce_hook(state: FusedHookState, bucket: dist.GradBucket) -> torch.futures.Future:
+def fused_allreduce_hook(
+    state: FusedHookState, bucket: dist.GradBucket
+) -> torch.futures.Future[torch.Tensor]:
     """DDP communication hook: average the bucket with scale and cast fused.
 
     DDP does not pre-divide gradients when a hook is registered, so the kernels
