@@ -69,48 +69,102 @@ bool adjacent(const std::vector<at::Tensor>& ts) {
 // ---------------------------------------------------------------------------
 // Work
 // ---------------------------------------------------------------------------
-WorkFairring::WorkFairring(c10d::OpType op, c10::intrusive_ptr<c10::ivalue::Future> future,
-                           std::shared_ptr<Engine> engine, bool blocking,
+WorkFairring::WorkFairring(c10d::OpType op, std::shared_ptr<Engine> engine, int device,
+                           std::vector<at::Tensor> result, bool blocking,
                            std::chrono::milliseconds default_timeout)
-    : c10d::Work(-1, op), future_(std::move(future)), engine_(std::move(engine)),
-      blocking_(blocking), default_timeout_(default_timeout) {}
+    : c10d::Work(-1, op), engine_(std::move(engine)), device_(device), result_(std::move(result)),
+      blocking_(blocking), default_timeout_(default_timeout) {
+  if (!engine_) enqueued_ = true;  // nothing to wait for (CPU path, world of one)
+}
+
+void WorkFairring::markEnqueued(cudaEvent_t done, cudaStream_t join) {
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    done_ = done;
+    join_ = join;
+    enqueued_ = true;
+    if (future_) completeFuture();
+  }
+  cv_.notify_all();
+}
+
+void WorkFairring::markFailed(std::exception_ptr e) {
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    error_ = e;
+    enqueued_ = true;
+    if (future_) future_->setError(e);
+  }
+  cv_.notify_all();
+}
+
+void WorkFairring::waitEnqueued() {
+  std::unique_lock<std::mutex> lk(mu_);
+  cv_.wait(lk, [&] { return enqueued_; });
+  if (error_) std::rethrow_exception(error_);
+}
+
+void WorkFairring::completeFuture() {
+  if (done_ == nullptr) {
+    future_->markCompleted(c10::IValue(result_));
+    return;
+  }
+  // The Future records its own event on the "current" stream: make that the
+  // side stream the collective finished on.
+  const c10::DeviceIndex di = static_cast<c10::DeviceIndex>(device_);
+  c10::cuda::CUDAGuard g(di);
+  c10::cuda::CUDAStreamGuard sg(c10::cuda::getStreamFromExternal(join_, di));
+  future_->markCompleted(c10::IValue(result_));
+}
+
+c10::intrusive_ptr<c10::ivalue::Future> WorkFairring::getFuture() {
+  std::lock_guard<std::mutex> lk(mu_);
+  if (!future_) {
+    std::vector<c10::Device> devs;
+    if (engine_) devs.emplace_back(at::kCUDA, static_cast<c10::DeviceIndex>(device_));
+    future_ = c10::make_intrusive<c10::ivalue::Future>(
+        c10::ListType::create(c10::TensorType::get()), devs);
+    if (enqueued_) {
+      if (error_)
+        future_->setError(error_);
+      else
+        completeFuture();
+    }
+  }
+  return future_;
+}
 
 bool WorkFairring::isCompleted() {
-  if (!future_->completed()) return false;
-  cudaEvent_t e = done_.load();
-  if (e == nullptr) return true;
-  cudaError_t q = cudaEventQuery(e);
+  std::lock_guard<std::mutex> lk(mu_);
+  if (!enqueued_) return false;
+  if (done_ == nullptr) return true;
+  cudaError_t q = cudaEventQuery(done_);
   if (q == cudaErrorNotReady) {
     (void)cudaGetLastError();
     return false;
   }
   return true;
 }
-bool WorkFairring::isSuccess() const { return future_->completed() && !future_->hasError(); }
-std::exception_ptr WorkFairring::exception() const {
-  return future_->completed() && future_->hasError() ? future_->exception_ptr() : nullptr;
-}
-std::vector<at::Tensor> WorkFairring::result() { return future_->value().toTensorVector(); }
+bool WorkFairring::isSuccess() const { return enqueued_ && !error_; }
+std::exception_ptr WorkFairring::exception() const { return error_; }
+std::vector<at::Tensor> WorkFairring::result() { return result_; }
 void WorkFairring::synchronize() { wait(kNoTimeout); }
-c10::intrusive_ptr<c10::ivalue::Future> WorkFairring::getFuture() { return future_; }
 void WorkFairring::abort() {
   if (engine_) engine_->abort();
-}
-void WorkFairring::setDoneEvent(cudaEvent_t e, int device) {
-  device_ = device;
-  done_.store(e);
 }
 
 bool WorkFairring::wait(std::chrono::milliseconds timeout) {
   // Host: until the kernels are enqueued (immediate unless a command thread is
   // used).  Device: the caller's current stream is made to wait for them.
-  future_->wait();
-  cudaEvent_t e = done_.load();
-  if (e != nullptr && engine_ && (blocking_ || timeout != kNoTimeout)) {
+  waitEnqueued();
+  if (done_ == nullptr || !engine_) return true;
+  const c10::DeviceIndex di = static_cast<c10::DeviceIndex>(device_);
+  C10_CUDA_CHECK(cudaStreamWaitEvent(c10::cuda::getCurrentCUDAStream(di).stream(), done_, 0));
+  if (blocking_ || timeout != kNoTimeout) {
     const auto limit = timeout != kNoTimeout ? timeout : default_timeout_;
     const auto t0 = std::chrono::steady_clock::now();
     for (;;) {
-      cudaError_t q = cudaEventQuery(e);
+      cudaError_t q = cudaEventQuery(done_);
       if (q == cudaSuccess) break;
       TORCH_CHECK(q == cudaErrorNotReady, "fairring: CUDA error while waiting: ",
                   cudaGetErrorString(q));
@@ -279,9 +333,8 @@ c10::intrusive_ptr<c10d::Backend> BackendFairring::delegateFor(const std::vector
 
 c10::intrusive_ptr<c10d::Work> BackendFairring::completedWork(c10d::OpType type,
                                                               std::vector<at::Tensor> result) {
-  auto fut = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
-  fut->markCompleted(c10::IValue(std::move(result)));
-  return c10::make_intrusive<WorkFairring>(type, fut, nullptr, false, options_->timeout);
+  return c10::make_intrusive<WorkFairring>(type, nullptr, -1, std::move(result), false,
+                                           options_->timeout);
 }
 
 c10::intrusive_ptr<c10d::Work> BackendFairring::runGpu(c10d::OpType type, const CollectiveDesc& d,
@@ -290,32 +343,31 @@ c10::intrusive_ptr<c10d::Work> BackendFairring::runGpu(c10d::OpType type, const 
                                                        std::function<void()> epilogue) {
   auto engine = engine_;
   const c10::DeviceIndex di = static_cast<c10::DeviceIndex>(engine_device_);
-  const at::Device dev(at::kCUDA, di);
-  c10::cuda::CUDAGuard guard(dev);
+  c10::cuda::CUDAGuard guard(di);
   const auto cur = c10::cuda::getCurrentCUDAStream(di);
   cudaEvent_t after = engine->begin(cur.stream());
-  auto fut = c10::make_intrusive<c10::ivalue::Future>(
-      c10::ListType::create(c10::TensorType::get()), std::vector<c10::Device>{dev});
-  auto work = c10::make_intrusive<WorkFairring>(type, fut, engine, options_->blocking_wait,
-                                                options_->timeout);
-  // The tensors are used on the engine's side streams: tell the caching
-  // allocator, as the reference does for its stage streams (device.cc:297-301).
-  for (const auto& t : keep)
-    for (cudaStream_t s : engine->streams())
-      c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(),
-                                                    c10::cuda::getStreamFromExternal(s, di));
+  auto work = c10::make_intrusive<WorkFairring>(type, engine, (int)di, std::move(result),
+                                                options_->blocking_wait, options_->timeout);
   const bool async = engine->config().command_thread;
   auto job = [=]() {
     try {
-      c10::cuda::CUDAGuard g2(dev);
-      cudaStream_t s = engine->run(d, after);
-      c10::cuda::CUDAStreamGuard sg(c10::cuda::getStreamFromExternal(s, di));
-      if (epilogue) epilogue();
-      work->setDoneEvent(engine->begin(s), di);
-      fut->markCompleted(c10::IValue(result));
+      c10::cuda::CUDAGuard g2(di);
+      std::vector<cudaStream_t> used;
+      cudaStream_t s = engine->run(d, after, &used);
+      // The tensors are used on side streams: tell the caching allocator, as
+      // the reference does for its stage streams (device.cc:297-301).
+      for (const auto& t : keep)
+        for (cudaStream_t u : used)
+          c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(),
+                                                        c10::cuda::getStreamFromExternal(u, di));
+      if (epilogue) {
+        c10::cuda::CUDAStreamGuard sg(c10::cuda::getStreamFromExternal(s, di));
+        epilogue();
+      }
+      work->markEnqueued(engine->begin(s), s);
     } catch (...) {
+      work->markFailed(std::current_exception());
       if (!async) throw;
-      fut->setError(std::current_exception());
     }
   };
   try {

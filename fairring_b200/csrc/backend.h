@@ -16,6 +16,7 @@
 #include <torch/csrc/distributed/c10d/Store.hpp>
 #include <torch/csrc/distributed/c10d/Work.hpp>
 
+#include <condition_variable>
 #include <functional>
 #include <map>
 #include <memory>
@@ -59,10 +60,15 @@ struct OptionsFairring : c10d::Backend::Options {
 
 class BackendFairring;
 
+// Completion of a collective is a CUDA event on one of the engine's side
+// streams: wait() makes the caller's current stream wait for it and returns
+// without blocking the host (like NCCL's work objects).  A CUDA-aware Future is
+// only built when somebody asks for one (DDP does); the reference always goes
+// through a Future (fairring/process_group.cc:35-75).
 class WorkFairring : public c10d::Work {
  public:
-  WorkFairring(c10d::OpType op, c10::intrusive_ptr<c10::ivalue::Future> future,
-               std::shared_ptr<Engine> engine, bool blocking,
+  WorkFairring(c10d::OpType op, std::shared_ptr<Engine> engine, int device,
+               std::vector<at::Tensor> result, bool blocking,
                std::chrono::milliseconds default_timeout);
   bool isCompleted() override;
   bool isSuccess() const override;
@@ -73,16 +79,26 @@ class WorkFairring : public c10d::Work {
   void abort() override;
   c10::intrusive_ptr<c10::ivalue::Future> getFuture() override;
 
-  // Set by the enqueueing code once the completion event has been recorded.
-  void setDoneEvent(cudaEvent_t e, int device);
+  // Called by the enqueueing code (caller's thread, or the command thread).
+  void markEnqueued(cudaEvent_t done, cudaStream_t join);
+  void markFailed(std::exception_ptr e);
 
  private:
-  c10::intrusive_ptr<c10::ivalue::Future> future_;
+  void waitEnqueued();
+  void completeFuture();  // mu_ held
+
   std::shared_ptr<Engine> engine_;
+  int device_;
+  std::vector<at::Tensor> result_;
   bool blocking_;
   std::chrono::milliseconds default_timeout_;
-  std::atomic<cudaEvent_t> done_{nullptr};
-  int device_ = -1;
+  std::mutex mu_;
+  std::condition_variable cv_;
+  bool enqueued_ = false;
+  cudaEvent_t done_ = nullptr;
+  cudaStream_t join_ = nullptr;
+  std::exception_ptr error_;
+  c10::intrusive_ptr<c10::ivalue::Future> future_;
 };
 
 using DelegateFactory = std::function<c10::intrusive_ptr<c10d::Backend>(const std::string&)>;

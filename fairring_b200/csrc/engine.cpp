@@ -368,7 +368,8 @@ void Engine::runAllreduceSlice(Channel& ch, const CollectiveDesc& d, const void*
   }
 }
 
-cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after) {
+cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after,
+                         std::vector<cudaStream_t>* used_streams) {
   std::lock_guard<std::mutex> lk(mu_);
   checkHealth();
   FR_CHECK(comboSupported(d.io, d.wire), "no kernel for this (tensor dtype, wire dtype) pair");
@@ -453,6 +454,8 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after) {
     Channel& ch = take();
     return ch.stream;
   }
+  if (used_streams)
+    for (int c : used) used_streams->push_back(channels_[c].stream);
   Channel& join = channels_[used[0]];
   for (size_t i = 1; i < used.size(); ++i) {
     Channel& ch = channels_[used[i]];

@@ -99,7 +99,9 @@ class Engine {
   cudaEvent_t begin(cudaStream_t caller);
   // Enqueue the whole collective.  Returns the side stream on which everything
   // it launched is ordered; the caller records its completion event there.
-  cudaStream_t run(const CollectiveDesc& d, cudaEvent_t after);
+  // `used` (optional) receives every side stream the collective touched.
+  cudaStream_t run(const CollectiveDesc& d, cudaEvent_t after,
+                   std::vector<cudaStream_t>* used_streams = nullptr);
   // Run `fn` now, or on the command thread when one is configured.
   void submit(std::function<void()> fn);
 
