@@ -169,8 +169,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       "detect_deployment",
       [](const c10::intrusive_ptr<c10d::Store>& store, int rank, int world, int gpus_per_machine,
          bool favorable, const std::string& boot_id) {
-        StoreAdapter s(store, "fairring/");
-        Deployment d = detectDeployment(s, rank, world, gpus_per_machine, favorable, boot_id);
+        Deployment d;
+        {
+          py::gil_scoped_release nogil;  // blocks on the store until all ranks have published
+          StoreAdapter s(store, "fairring/");
+          d = detectDeployment(s, rank, world, gpus_per_machine, favorable, boot_id);
+        }
         return py::dict(py::arg("D") = d.topo.D, py::arg("M") = d.topo.M,
                         py::arg("favorable") = d.topo.favorable, py::arg("m") = d.topo.m,
                         py::arg("d") = d.topo.d, py::arg("num_hosts") = d.num_hosts,
@@ -178,8 +182,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         py::arg("single_host") = d.single_host);
       },
       py::arg("store"), py::arg("rank"), py::arg("world"), py::arg("gpus_per_machine") = 0,
-      py::arg("favorable") = false, py::arg("boot_id") = "",
-      py::call_guard<py::gil_scoped_release>());
+      py::arg("favorable") = false, py::arg("boot_id") = "");
 
   m.def("emulated_collective", &emulatedCollective, py::arg("kind"), py::arg("inputs"),
         py::arg("gpus_per_machine"), py::arg("favorable") = false, py::arg("op") = "sum",
