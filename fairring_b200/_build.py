@@ -42,6 +42,7 @@ SOURCES = [
     "kernels/collectives_f32_bf16.cu",
     "kernels/collectives_f32_f16.cu",
     "kernels/local_ops.cu",
+    "kernels/noalloc_allreduce.cu",
 ]
 
 NVCC_FLAGS = [
