@@ -22,7 +22,7 @@ FAIRRING_PARALLELISM           slices in flight = side streams/channels (default
 FAIRRING_SLICE_SIZE            max bytes per slice (default 25 MiB, DDP's bucket size)
 FAIRRING_GPUS_PER_MACHINE      D of the M x D grouping (default: all ranks of a host)
 FAIRRING_RANK_LAYOUT           "standard" (rank = m*D+d) or "favorable" (rank = d*M+m)
-FAIRRING_ALGO                  auto | oneshot | twoshot | hier | nvls | nvls_oneshot
+FAIRRING_ALGO                  auto | oneshot | twoshot | hier | nvls | nvls_oneshot | bounce
 FAIRRING_BLOCKS                thread blocks per kernel (SM budget, default 32, max 64)
 FAIRRING_ONESHOT_MAX           largest message (bytes) for the one-shot kernel
 FAIRRING_NVLS                  auto | on | off   (NVSwitch multicast kernels)
@@ -31,6 +31,10 @@ FAIRRING_NVLS_ONESHOT_MAX      largest message (bytes) for the NVLS one-shot ker
 FAIRRING_TRANSPORT             auto | vmm | ipc  (how peer memory is shared)
 FAIRRING_DIRECT                auto | nvls | p2p | off  (in-place kernels for tensors from
                                ``symmetric_empty``: no staging copies)
+FAIRRING_BOUNCE                auto | on | off  (big ordinary tensors: copy engines move them
+                               through a symmetric bounce buffer that is reduced in place;
+                               takes a third of the memory budget)
+FAIRRING_BOUNCE_MIN            smallest message (bytes) for the bounce path (default 8 MiB)
 FAIRRING_DEVICE_TIMEOUT_MS     limit of one device-side wait on a peer (default 30000)
 FAIRRING_COMMAND_THREAD        1: enqueue kernels from a dedicated thread
 FAIRRING_BLOCKING_WAIT         1: Work.wait() blocks the host and reports kernel failures
@@ -111,6 +115,8 @@ def options_from_env(timeout: timedelta | None = None) -> "_C.Options":
     opts.nvls = os.environ.get("FAIRRING_NVLS", "auto").lower()
     opts.transport = os.environ.get("FAIRRING_TRANSPORT", "auto").lower()
     opts.direct = os.environ.get("FAIRRING_DIRECT", "auto").lower()
+    opts.bounce = os.environ.get("FAIRRING_BOUNCE", "auto").lower()
+    opts.bounce_min_bytes = _env_int("FAIRRING_BOUNCE_MIN", opts.bounce_min_bytes)
     opts.command_thread = os.environ.get("FAIRRING_COMMAND_THREAD", "0") == "1"
     opts.blocking_wait = os.environ.get("FAIRRING_BLOCKING_WAIT", "0") == "1"
     opts.boot_id_override = os.environ.get("FAIRRING_BOOT_ID", "")

@@ -25,7 +25,7 @@ def main(argv=None) -> int:
     ap.add_argument("--sizes", default="1048576,16777216,134217728")
     ap.add_argument("--blocks", default="16,32,64")
     ap.add_argument("--channels", default="2,4,8")
-    ap.add_argument("--variants", default="twoshot,nvls,sym_p2p,sym_nvls")
+    ap.add_argument("--variants", default="twoshot,nvls,bounce,sym_p2p,sym_nvls")
     ap.add_argument("--dtype", default="fp32")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--nccl", action="store_true", help="also time NCCL on the same buffers")
@@ -84,7 +84,7 @@ def main(argv=None) -> int:
             continue
         os.environ["FAIRRING_BLOCKS"] = str(blocks)
         os.environ["FAIRRING_PARALLELISM"] = str(channels)
-        os.environ["FAIRRING_ALGO"] = {"twoshot": "twoshot", "nvls": "nvls"}.get(variant, "auto")
+        os.environ["FAIRRING_ALGO"] = {"twoshot": "twoshot", "nvls": "nvls", "bounce": "bounce"}.get(variant, "auto")
         os.environ["FAIRRING_DIRECT"] = {"sym_p2p": "p2p", "sym_nvls": "nvls"}.get(variant, "off")
         os.environ["FAIRRING_ONESHOT_MAX"] = "0"
         g = dist.new_group(backend="fairring")

@@ -261,6 +261,8 @@ std::shared_ptr<Engine> BackendFairring::ensureEngine(int device) {
   cfg.transport = parseTransport(options_->transport);
   cfg.nvls = parseNvls(options_->nvls);
   cfg.direct = options_->direct;
+  cfg.bounce = options_->bounce;
+  cfg.bounce_min_bytes = options_->bounce_min_bytes;
   cfg.bootstrap_timeout = options_->timeout;
   c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
   engine_ = std::make_shared<Engine>(std::make_shared<StoreAdapter>(store_, "fairring/gpu/"),
@@ -724,6 +726,7 @@ std::map<std::string, int64_t> BackendFairring::stats() {
     m["gpu_collectives"] = (int64_t)s.collectives;
     m["gpu_slices"] = (int64_t)s.slices;
     m["gpu_wire_bytes"] = (int64_t)s.wire_bytes;
+    m["gpu_bounce_slices"] = (int64_t)s.bounce_slices;
     for (int k = 0; k < (int)KernelId::kCount; ++k)
       m[std::string("launch_") + kernelName((KernelId)k)] = (int64_t)s.launches[k];
     m["nvls"] = engine_->nvlsAvailable() ? 1 : 0;

@@ -70,6 +70,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("nvls", &OptionsFairring::nvls)
       .def_readwrite("transport", &OptionsFairring::transport)
       .def_readwrite("direct", &OptionsFairring::direct)
+      .def_readwrite("bounce", &OptionsFairring::bounce)
+      .def_readwrite("bounce_min_bytes", &OptionsFairring::bounce_min_bytes)
       .def_readwrite("command_thread", &OptionsFairring::command_thread)
       .def_readwrite("blocking_wait", &OptionsFairring::blocking_wait)
       .def_readwrite("boot_id_override", &OptionsFairring::boot_id_override)

@@ -16,15 +16,17 @@ const char* algoName(Algo a) {
     case Algo::HIER: return "hier";
     case Algo::NVLS: return "nvls";
     case Algo::NVLS_ONESHOT: return "nvls_oneshot";
+    case Algo::BOUNCE: return "bounce";
   }
   return "?";
 }
 
 Algo parseAlgo(const std::string& s) {
-  for (Algo a : {Algo::AUTO, Algo::ONESHOT, Algo::TWOSHOT, Algo::HIER, Algo::NVLS, Algo::NVLS_ONESHOT})
+  for (Algo a : {Algo::AUTO, Algo::ONESHOT, Algo::TWOSHOT, Algo::HIER, Algo::NVLS, Algo::NVLS_ONESHOT,
+                 Algo::BOUNCE})
     if (s == algoName(a)) return a;
   FR_CHECK(false, "unknown FAIRRING_ALGO '", s,
-           "' (auto, oneshot, twoshot, hier, nvls, nvls_oneshot)");
+           "' (auto, oneshot, twoshot, hier, nvls, nvls_oneshot, bounce)");
   return Algo::AUTO;
 }
 
@@ -68,14 +70,20 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
   FR_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_));
   const int max_channels = std::max(1, sms / cfg_.blocks);
   if (cfg_.parallelism > max_channels) cfg_.parallelism = max_channels;
-  plan_ = planMemory(cfg_.total_memory, cfg_.slice_bytes, cfg_.parallelism, topo_.world,
-                     cfg_.min_half_bytes);
+  const bool want_bounce = cfg_.bounce != "off" && topo_.world > 1 && topo_.M == 1;
+  // With bounce buffers the budget is cut in three equal parts per channel:
+  // the two staging halves and the bounce buffer.
+  plan_ = planMemory(want_bounce ? cfg_.total_memory / 3 * 2 : cfg_.total_memory, cfg_.slice_bytes,
+                     cfg_.parallelism, topo_.world, cfg_.min_half_bytes);
 
   alloc_.reset(new SymmAllocator(store_, topo_.rank, topo_.world, device_, cfg_.transport,
                                  cfg_.nvls, cfg_.bootstrap_timeout));
   flags_bytes_ = (size_t)roundUp((int64_t)(kFlagPadBytes * plan_.channels), 64 << 10);
   region_ = alloc_->allocate(flags_bytes_ + (size_t)plan_.slot_bytes * plan_.channels,
                              /*want_multicast=*/true);
+
+  if (want_bounce)
+    bounce_ = alloc_->allocate((size_t)plan_.half_bytes * plan_.channels, /*want_multicast=*/true);
 
   FR_CUDA(cudaMalloc(&seq_dev_, sizeof(uint32_t) * kMaxBlocks * plan_.channels));
   FR_CUDA(cudaMemset(seq_dev_, 0, sizeof(uint32_t) * kMaxBlocks * plan_.channels));
@@ -140,6 +148,7 @@ Engine::~Engine() {
   cudaDeviceSynchronize();
   try {
     for (auto& r : user_regions_) alloc_->release(r);
+    alloc_->release(bounce_);
     alloc_->release(region_);
   } catch (const std::exception&) {
   }
@@ -285,6 +294,56 @@ bool Engine::runDirect(const CollectiveDesc& d, const std::function<Channel&()>&
   return true;
 }
 
+// Ordinary tensor, big message: copy engine in -> in-place kernel on the
+// symmetric bounce buffer -> copy engine out, all on the channel's stream.  The
+// kernel's closing barrier means every peer is done with this rank's buffer
+// before the copy-out (and the next copy-in) touches it, so one buffer per
+// channel is enough.
+bool Engine::runBounce(const CollectiveDesc& d, const std::function<Channel&()>& take) {
+  if (bounce_.ptrs.empty() || d.kind != CollKind::ALLREDUCE) return false;
+  if (d.io != d.wire || d.scale != 1.0f) return false;  // the fused kernels do scale and cast
+  const bool forced = cfg_.algo == Algo::BOUNCE;
+  if (!forced && cfg_.algo != Algo::AUTO) return false;
+  const int es = dtypeSize(d.io);
+  const int64_t bytes = d.numel * es;
+  if (!forced && bytes < cfg_.bounce_min_bytes) return false;
+  if (bytes <= cfg_.oneshot_max_bytes) return false;
+  const bool nvls = bounce_.mc_ptr != nullptr && nvlsSupported(d.wire, d.op) && cfg_.direct != "p2p";
+  const int W = topo_.world;
+  const int64_t V = kVecBytes / es;
+  int64_t cap = std::max<int64_t>(cfg_.direct_min_slice_bytes,
+                                  ceilDiv(bytes, (int64_t)channels_.size()));
+  if (cap > plan_.half_bytes) cap = plan_.half_bytes;
+  int64_t slice_elems = roundDown(cap / es, V * W);
+  if (slice_elems < V * W) slice_elems = V * W;
+  const char* in = static_cast<const char*>(d.in);
+  char* out = static_cast<char*>(d.out);
+  for (int64_t start = 0; start < d.numel; start += slice_elems) {
+    const int64_t n = std::min(slice_elems, d.numel - start);
+    Channel& ch = take();
+    const size_t o = (size_t)(&ch - channels_.data()) * (size_t)plan_.half_bytes;
+    char* mine = static_cast<char*>(bounce_.ptrs[topo_.rank]) + o;
+    FR_CUDA(cudaMemcpyAsync(mine, in + start * es, (size_t)n * es, cudaMemcpyDeviceToDevice,
+                            ch.stream));
+    OpArgs a{};
+    a.seg = allreduceSeg(n, es, W);
+    a.scale = 1.0f;
+    a.op = (int32_t)d.op;
+    a.io_dtype = a.wire_dtype = (int32_t)d.io;
+    a.flags = kAdvanceSeq;
+    for (int r = 0; r < W; ++r) a.peer[r] = static_cast<char*>(bounce_.ptrs[r]) + o;
+    a.mc = nvls ? static_cast<char*>(bounce_.mc_ptr) + o : nullptr;
+    a.in[0] = a.out[0] = mine;
+    launch(ch, nvls ? KernelId::NVLS_DIRECT : KernelId::P2P_DIRECT, a);
+    FR_CUDA(cudaMemcpyAsync(out + start * es, mine, (size_t)n * es, cudaMemcpyDeviceToDevice,
+                            ch.stream));
+    ++stats_.slices;
+    ++stats_.bounce_slices;
+  }
+  stats_.wire_bytes += (uint64_t)bytes;
+  return true;
+}
+
 EngineStats Engine::stats() const { return stats_; }
 
 std::vector<cudaStream_t> Engine::streams() const {
@@ -300,7 +359,7 @@ std::string Engine::describe() const {
      << " transport=" << alloc_->describe() << " nvls=" << (nvlsAvailable() ? "yes" : "no")
      << " channels=" << plan_.channels << " half_slot=" << plan_.half_bytes
      << "B max_slice=" << plan_.max_slice_bytes << "B blocks=" << cfg_.blocks
-     << " algo=" << algoName(cfg_.algo);
+     << " algo=" << algoName(cfg_.algo) << " bounce=" << (bounce_.ptrs.empty() ? "no" : "yes");
   return os.str();
 }
 
@@ -312,6 +371,7 @@ Algo Engine::chooseAllreduce(int64_t wire_bytes, DType wire, RedOp op) const {
   Algo a = cfg_.algo;
   if (a == Algo::ONESHOT && !oneshot_fits) a = Algo::AUTO;
   if ((a == Algo::NVLS || a == Algo::NVLS_ONESHOT) && !nvls_ok) a = Algo::AUTO;
+  if (a == Algo::BOUNCE) a = Algo::AUTO;  // this message did not qualify for the bounce path
   if (a == Algo::TWOSHOT && topo_.M > 1) a = Algo::HIER;
   if (a != Algo::AUTO) return a;
   if (wire_bytes <= cfg_.oneshot_max_bytes && oneshot_fits) return Algo::ONESHOT;
@@ -389,7 +449,7 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after,
   char* out = static_cast<char*>(d.out);
   ++stats_.collectives;
 
-  if (runDirect(d, take)) {
+  if (runDirect(d, take) || runBounce(d, take)) {
     // nothing else to do
   } else if (d.kind == CollKind::ALLREDUCE) {
     const int64_t bytes = d.numel * wes;

@@ -29,7 +29,7 @@
 
 namespace fairring {
 
-enum class Algo : int32_t { AUTO = 0, ONESHOT, TWOSHOT, HIER, NVLS, NVLS_ONESHOT };
+enum class Algo : int32_t { AUTO = 0, ONESHOT, TWOSHOT, HIER, NVLS, NVLS_ONESHOT, BOUNCE };
 const char* algoName(Algo a);
 Algo parseAlgo(const std::string& s);
 
@@ -52,6 +52,12 @@ struct EngineConfig {
   // staging: "auto" (NVLS when possible, else peer loads), "p2p", "nvls", "off".
   std::string direct = "auto";
   int64_t direct_min_slice_bytes = 2ll << 20;  // a message is split over channels down to this
+  // Ordinary (non-symmetric) tensors of at least bounce_min_bytes can be moved
+  // into and out of a symmetric bounce buffer by the copy engines and reduced
+  // there in place: the SMs only run the in-place kernel.  "auto" | "on" | "off".
+  // A third of the memory budget becomes bounce buffers when this is enabled.
+  std::string bounce = "auto";
+  int64_t bounce_min_bytes = 8ll << 20;
   std::chrono::milliseconds bootstrap_timeout{120000};
 };
 
@@ -72,6 +78,7 @@ struct EngineStats {
   uint64_t collectives = 0;
   uint64_t slices = 0;
   uint64_t wire_bytes = 0;
+  uint64_t bounce_slices = 0;
   std::array<uint64_t, (size_t)KernelId::kCount> launches{};
 };
 
@@ -140,6 +147,7 @@ class Engine {
   cudaEvent_t nextEvent();
   bool findSymmetric(const void* p, size_t bytes, const SymmRegion** reg, size_t* off) const;
   bool runDirect(const CollectiveDesc& d, const std::function<Channel&()>& take);
+  bool runBounce(const CollectiveDesc& d, const std::function<Channel&()>& take);
 
   std::shared_ptr<KvStore> store_;
   Topo topo_;
@@ -149,6 +157,7 @@ class Engine {
   std::unique_ptr<SymmAllocator> alloc_;
   SymmRegion region_;
   std::vector<SymmRegion> user_regions_;
+  SymmRegion bounce_;  // [channels][half_bytes], empty when disabled
   size_t flags_bytes_ = 0;
   uint32_t* seq_dev_ = nullptr;
   uint32_t* status_host_ = nullptr;  // pinned + mapped: [channels][kStatusWords], then abort word

@@ -67,6 +67,12 @@ def _suite(rank, world, check_ddp):
     for i, b in enumerate(bufs):
         assert float(b[0]) == sum(r + i for r in range(world)) and float(b[-1]) == float(b[0])
 
+    # a big ordinary tensor (copy-engine bounce path when enabled), odd length
+    x = seeded(12_000_001, torch.float32, rank, 9).to(dev)
+    dist.all_reduce(x)
+    expect = torch.stack([seeded(12_000_001, torch.float32, r, 9).double() for r in range(world)]).sum(0)
+    torch.testing.assert_close(x.double().cpu(), expect, rtol=1e-4, atol=1e-4)
+
     # fused scale + bf16 wire
     g = seeded(1_000_003, torch.float32, rank, 77).to(dev)
     be.allreduce_fused(g, 1.0 / world, torch.bfloat16, "sum").wait()
@@ -169,6 +175,8 @@ CONFIGS = {
     "twoshot_no_nvls": {"FAIRRING_NVLS": "off", "FAIRRING_ALGO": "twoshot"},
     "nvls": {"FAIRRING_ALGO": "nvls"},
     "nvls_oneshot": {"FAIRRING_ALGO": "nvls_oneshot"},
+    "bounce": {"FAIRRING_ALGO": "bounce"},
+    "bounce_p2p": {"FAIRRING_ALGO": "bounce", "FAIRRING_NVLS": "off"},
     "hier_three_kernels": {"FAIRRING_ALGO": "hier", "FAIRRING_NVLS": "off"},
     "ipc_transport_cmd_thread": {"FAIRRING_TRANSPORT": "ipc", "FAIRRING_COMMAND_THREAD": "1"},
     "machines_of_one_gpu": {"FAIRRING_GPUS_PER_MACHINE": "1", "FAIRRING_NVLS": "off"},
@@ -192,6 +200,8 @@ def test_backend_on_gpus(name):
         assert stats["nvls"] == 0 and stats["launch_twoshot_allreduce"] > 0
     if name in ("nvls", "nvls_oneshot") and stats["nvls"] == 1:
         assert stats["launch_nvls_allreduce"] + stats["launch_nvls_oneshot_allreduce"] > 0
+    if name.startswith("bounce"):
+        assert stats["gpu_bounce_slices"] > 0
     if name == "hier_three_kernels":
         assert stats["launch_rs_intragroup"] > 0 and stats["launch_ag_intragroup"] > 0
     if name == "machines_of_one_gpu":
