@@ -23,7 +23,11 @@ FAIRRING_SLICE_SIZE            max bytes per slice (default 25 MiB, DDP's bucket
 FAIRRING_GPUS_PER_MACHINE      D of the M x D grouping (default: all ranks of a host)
 FAIRRING_RANK_LAYOUT           "standard" (rank = m*D+d) or "favorable" (rank = d*M+m)
 FAIRRING_ALGO                  auto | oneshot | twoshot | hier | nvls | nvls_oneshot | bounce
-FAIRRING_BLOCKS                thread blocks per kernel (SM budget, default 32, max 64)
+FAIRRING_BLOCKS                thread blocks per kernel (default 16, max 64)
+FAIRRING_SM_BUDGET             SMs the collectives may occupy at once (default 64): the number
+                               of channels is at most SM_BUDGET / BLOCKS.  Raise it (up to the
+                               SM count) for stand-alone all-reduce bandwidth, keep it low to
+                               leave the GPU to backward
 FAIRRING_ONESHOT_MAX           largest message (bytes) for the one-shot kernel
 FAIRRING_NVLS                  auto | on | off   (NVSwitch multicast kernels)
 FAIRRING_NVLS_MIN              smallest message (bytes) for the NVLS two-shot kernel
@@ -34,7 +38,7 @@ FAIRRING_DIRECT                auto | nvls | p2p | off  (in-place kernels for te
 FAIRRING_BOUNCE                auto | on | off  (big ordinary tensors: copy engines move them
                                through a symmetric bounce buffer that is reduced in place;
                                takes a third of the memory budget)
-FAIRRING_BOUNCE_MIN            smallest message (bytes) for the bounce path (default 8 MiB)
+FAIRRING_BOUNCE_MIN            smallest message (bytes) for the bounce path (default 64 MiB)
 FAIRRING_DEVICE_TIMEOUT_MS     limit of one device-side wait on a peer (default 30000)
 FAIRRING_COMMAND_THREAD        1: enqueue kernels from a dedicated thread
 FAIRRING_BLOCKING_WAIT         1: Work.wait() blocks the host and reports kernel failures
@@ -108,6 +112,7 @@ def options_from_env(timeout: timedelta | None = None) -> "_C.Options":
     opts.favorable_layout = layout == "favorable"
     opts.algo = os.environ.get("FAIRRING_ALGO", "auto").lower()
     opts.blocks = _env_int("FAIRRING_BLOCKS", opts.blocks)
+    opts.sm_budget = _env_int("FAIRRING_SM_BUDGET", opts.sm_budget)
     opts.oneshot_max_bytes = _env_int("FAIRRING_ONESHOT_MAX", opts.oneshot_max_bytes)
     opts.nvls_min_bytes = _env_int("FAIRRING_NVLS_MIN", opts.nvls_min_bytes)
     opts.nvls_oneshot_max_bytes = _env_int("FAIRRING_NVLS_ONESHOT_MAX", opts.nvls_oneshot_max_bytes)

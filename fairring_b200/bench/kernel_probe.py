@@ -1,0 +1,103 @@
+"""Run ONE kernel of the library a few times on one GPU and report its device
+time (for roofline arithmetic, and as the small, self-ending workload to put
+under ``ncu``).
+
+    python -m fairring_b200.bench.kernel_probe --kernel twoshot --world 8 --mib 16
+    python -m fairring_b200.bench.kernel_probe --kernel adamw --mib 256
+
+Collective kernels run with all ``--world`` ranks emulated on this GPU (one
+cooperative launch, grid.y = rank), so "peer" traffic is local HBM traffic: the
+numbers characterise the kernel's memory pipeline, not NVLink.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="twoshot",
+                    choices=["oneshot", "twoshot", "hier", "direct", "adamw", "sumsq"])
+    ap.add_argument("--world", type=int, default=8)
+    ap.add_argument("--gpus-per-machine", type=int, default=0, help="hier: group size (default world/2)")
+    ap.add_argument("--mib", type=float, default=16.0, help="message (or buffer) size per rank, MiB")
+    ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--blocks", type=int, default=16)
+    ap.add_argument("--iters", type=int, default=3)
+    args = ap.parse_args(argv)
+
+    from torch.profiler import ProfilerActivity, profile
+
+    import fairring_b200
+
+    C = fairring_b200._C
+    torch.cuda.set_device(0)
+    dtype = torch.float32 if args.dtype == "fp32" else torch.bfloat16
+    es = 4 if args.dtype == "fp32" else 2
+    n = int(args.mib * (1 << 20)) // es
+    n -= n % (4 * args.world * 16)
+    W = args.world
+
+    if args.kernel in ("adamw", "sumsq"):
+        p, g = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+        m, v = torch.zeros_like(p), torch.zeros_like(p)
+        if args.kernel == "adamw":
+            fn = lambda i: C.adamw_flat_(p, g, m, v, 1e-3, 0.9, 0.95, 1e-8, 0.1, i + 1, 1.0)  # noqa: E731
+            algo_bytes = n * 4 * 7  # read p,g,m,v; write p,m,v
+            pattern = "adamw_flat"
+        else:
+            fn = lambda i: C.sumsq(g)  # noqa: E731
+            algo_bytes = n * 4
+            pattern = "sumsq"
+    else:
+        ins = [torch.randn(n, device="cuda").to(dtype) for _ in range(W)]
+        gpm = W
+        if args.kernel == "hier":
+            gpm = args.gpus_per_machine or max(1, W // 2)
+        half = max(1 << 20, W * n * es if args.kernel == "oneshot" else n * es)
+        fn = lambda i: C.emulated_collective(  # noqa: E731
+            "allreduce", ins, gpm, algo=args.kernel, blocks=args.blocks, half_bytes=half)
+        nb = n * es
+        # HBM bytes the algorithm has to move, summed over the W emulated ranks.
+        per_rank = {"oneshot": nb * (1 + W) + nb * W + nb,      # read in, write W copies; read W, write out
+                    "twoshot": 2 * nb + (nb + nb / W) + 2 * nb,  # push; reduce; gather
+                    "hier": 2 * nb + (nb + nb / W) + 2 * nb,     # (plus the shard-server pass when M > 1)
+                    "direct": nb + nb}[args.kernel]              # read every copy of own chunk, write every copy
+        algo_bytes = per_rank * W
+        pattern = {"oneshot": "oneshot_allreduce", "twoshot": "twoshot_allreduce",
+                   "hier": "rs_intragroup|shard_server_reduce|ag_intragroup",
+                   "direct": "direct_allreduce"}[args.kernel]
+
+    fn(0)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for i in range(args.iters):
+            fn(i + 1)
+        torch.cuda.synchronize()
+    import re
+
+    total_us, calls = 0.0, 0
+    names = []
+    for e in prof.key_averages():
+        if re.search(pattern, e.key):
+            total_us += e.device_time_total
+            calls = max(calls, e.count)
+            names.append(e.key[:80])
+    per_call_us = total_us / max(1, args.iters)
+    print(json.dumps({
+        "kernel": args.kernel, "world": W, "bytes_per_rank": n * es, "dtype": args.dtype,
+        "blocks_per_rank": args.blocks, "device_us_per_call": round(per_call_us, 1),
+        "algorithmic_hbm_bytes": int(algo_bytes),
+        "achieved_gbs": round(algo_bytes / (per_call_us * 1e-6) / 1e9, 1) if per_call_us else None,
+        "kernels": names,
+    }))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -83,6 +83,7 @@ def main(argv=None) -> int:
         if blocks * channels > 144:
             continue
         os.environ["FAIRRING_BLOCKS"] = str(blocks)
+        os.environ["FAIRRING_SM_BUDGET"] = "148"
         os.environ["FAIRRING_PARALLELISM"] = str(channels)
         os.environ["FAIRRING_ALGO"] = {"twoshot": "twoshot", "nvls": "nvls", "bounce": "bounce"}.get(variant, "auto")
         os.environ["FAIRRING_DIRECT"] = {"sym_p2p": "p2p", "sym_nvls": "nvls"}.get(variant, "off")

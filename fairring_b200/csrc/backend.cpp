@@ -251,6 +251,7 @@ std::shared_ptr<Engine> BackendFairring::ensureEngine(int device) {
   cfg.slice_bytes = options_->slice_size_in_bytes;
   cfg.parallelism = (int32_t)options_->min_parallelism;
   cfg.blocks = (int32_t)options_->blocks;
+  cfg.sm_budget = (int32_t)options_->sm_budget;
   cfg.oneshot_max_bytes = options_->oneshot_max_bytes;
   cfg.nvls_min_bytes = options_->nvls_min_bytes;
   cfg.nvls_oneshot_max_bytes = options_->nvls_oneshot_max_bytes;

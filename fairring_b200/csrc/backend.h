@@ -45,7 +45,8 @@ struct OptionsFairring : c10d::Backend::Options {
   int64_t gpus_per_machine = 0;   // 0: one group per real host
   bool favorable_layout = false;  // numbering of virtual machines: d*M+m instead of m*D+d
   std::string algo = "auto";
-  int64_t blocks = 32;
+  int64_t blocks = 16;
+  int64_t sm_budget = 64;
   int64_t oneshot_max_bytes = 256 << 10;
   int64_t nvls_min_bytes = 0;
   int64_t nvls_oneshot_max_bytes = 2 << 20;
@@ -54,7 +55,7 @@ struct OptionsFairring : c10d::Backend::Options {
   std::string transport = "auto";  // auto | vmm | ipc
   std::string direct = "auto";     // auto | p2p | nvls | off: in-place path for symmetric tensors
   std::string bounce = "auto";     // auto | on | off: copy-engine bounce buffers for big plain tensors
-  int64_t bounce_min_bytes = 8ll << 20;
+  int64_t bounce_min_bytes = 64ll << 20;
   bool command_thread = false;
   bool blocking_wait = false;
   std::string boot_id_override;    // tests: pretend to be on another host

@@ -63,6 +63,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("favorable_layout", &OptionsFairring::favorable_layout)
       .def_readwrite("algo", &OptionsFairring::algo)
       .def_readwrite("blocks", &OptionsFairring::blocks)
+      .def_readwrite("sm_budget", &OptionsFairring::sm_budget)
       .def_readwrite("oneshot_max_bytes", &OptionsFairring::oneshot_max_bytes)
       .def_readwrite("nvls_min_bytes", &OptionsFairring::nvls_min_bytes)
       .def_readwrite("nvls_oneshot_max_bytes", &OptionsFairring::nvls_oneshot_max_bytes)

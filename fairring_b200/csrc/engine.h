@@ -38,7 +38,8 @@ struct EngineConfig {
   int64_t slice_bytes = 25ll << 20;    // FAIRRING_SLICE_SIZE
   int32_t parallelism = 16;            // FAIRRING_PARALLELISM: slices in flight
   int64_t min_half_bytes = 4ll << 20;  // channels are merged until a half-slot is at least this
-  int32_t blocks = 32;                 // thread blocks per kernel (SM budget)
+  int32_t blocks = 16;                 // thread blocks per kernel
+  int32_t sm_budget = 64;              // channels x blocks never exceeds this (nor the SM count)
   int64_t oneshot_max_bytes = 256 << 10;
   int64_t nvls_min_bytes = 0;          // below this the peer-load two-shot is used
   int64_t nvls_oneshot_max_bytes = 2 << 20;
@@ -57,7 +58,7 @@ struct EngineConfig {
   // there in place: the SMs only run the in-place kernel.  "auto" | "on" | "off".
   // A third of the memory budget becomes bounce buffers when this is enabled.
   std::string bounce = "auto";
-  int64_t bounce_min_bytes = 8ll << 20;
+  int64_t bounce_min_bytes = 64ll << 20;
   std::chrono::milliseconds bootstrap_timeout{120000};
 };
 
