@@ -756,6 +756,26 @@ std::map<std::string, int64_t> BackendFairring::deployment() {
           {"ranks_per_host", d.ranks_per_host}, {"single_host", d.single_host ? 1 : 0}};
 }
 
+std::vector<std::map<std::string, std::string>> BackendFairring::trace() {
+  std::lock_guard<std::mutex> lk(mu_);
+  std::vector<std::map<std::string, std::string>> out;
+  if (!engine_) return out;
+  static const char* kKinds[] = {"all_reduce", "reduce_scatter", "all_gather"};
+  for (const TraceEntry& t : engine_->trace()) {
+    std::map<std::string, std::string> m;
+    m["seq"] = std::to_string(t.seq);
+    m["kind"] = kKinds[t.kind];
+    m["bytes"] = std::to_string(t.bytes);
+    m["first_kernel"] = t.first_kernel >= 0 ? kernelName((KernelId)t.first_kernel) : "none";
+    m["launches"] = std::to_string(t.launches);
+    m["slices"] = std::to_string(t.slices);
+    m["channels"] = std::to_string(t.channels);
+    m["host_us"] = std::to_string(t.host_us);
+    out.push_back(std::move(m));
+  }
+  return out;
+}
+
 void BackendFairring::checkHealth() {
   std::shared_ptr<Engine> e;
   {

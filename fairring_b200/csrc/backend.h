@@ -185,6 +185,8 @@ class BackendFairring : public c10d::Backend {
   // all_reduce on (slices of) it runs in place without staging copies.
   at::Tensor symmetricEmpty(int64_t numel, at::ScalarType dtype);
   std::map<std::string, int64_t> deployment();
+  // The engine's record of the last collectives (kind, bytes, first kernel, launches, ...).
+  std::vector<std::map<std::string, std::string>> trace();
 
  private:
   enum class Route { OWN_GPU, OWN_CPU, DELEGATE };

@@ -112,6 +112,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("describe", &BackendFairring::describe, py::call_guard<py::gil_scoped_release>())
       .def("stats", &BackendFairring::stats, py::call_guard<py::gil_scoped_release>())
       .def("deployment", &BackendFairring::deployment, py::call_guard<py::gil_scoped_release>())
+      .def("trace", &BackendFairring::trace, py::call_guard<py::gil_scoped_release>())
       .def("check_health", &BackendFairring::checkHealth, py::call_guard<py::gil_scoped_release>())
       .def("reset", &BackendFairring::reset, py::call_guard<py::gil_scoped_release>())
       .def("abort", &BackendFairring::abort, py::call_guard<py::gil_scoped_release>())

@@ -4,6 +4,10 @@
 #include <cstring>
 #include <sstream>
 
+#include <nvtx3/nvToolsExt.h>
+
+#include <cstdlib>
+
 #include "check.h"
 
 namespace fairring {
@@ -49,6 +53,7 @@ std::function<void()> CommandQueue::pop() {
 namespace {
 constexpr size_t kFlagPadBytes = (size_t)kMaxRanks * kMaxBlocks * sizeof(uint32_t);
 constexpr int kEventPool = 2048;
+constexpr size_t kTraceLen = 256;
 }  // namespace
 
 Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
@@ -58,6 +63,7 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
            " ranks, got ", topo_.world);
   FR_CHECK(cfg_.blocks >= 1 && cfg_.blocks <= kMaxBlocks, "FAIRRING_BLOCKS must be in 1..",
            kMaxBlocks);
+  if (const char* e = std::getenv("FAIRRING_NVTX")) nvtx_ = e[0] == '1';
   FR_CUDA(cudaSetDevice(device_));
   // Kernels of different channels wait on their peers while resident.  If more
   // blocks were in flight than the GPU can hold at once, two GPUs could each
@@ -353,6 +359,14 @@ bool Engine::runBounce(const CollectiveDesc& d, const std::function<Channel&()>&
 
 EngineStats Engine::stats() const { return stats_; }
 
+std::vector<TraceEntry> Engine::trace() const {
+  std::vector<TraceEntry> out;
+  const uint64_t n = stats_.collectives;
+  const uint64_t first = n > kTraceLen ? n - kTraceLen : 0;
+  for (uint64_t i = first; i < n && i - first < trace_.size(); ++i) out.push_back(trace_[i % kTraceLen]);
+  return out;
+}
+
 std::vector<cudaStream_t> Engine::streams() const {
   std::vector<cudaStream_t> v;
   for (auto& ch : channels_) v.push_back(ch.stream);
@@ -395,6 +409,8 @@ void Engine::launch(Channel& ch, KernelId id, const OpArgs& a) {
                                    ch.stream);
   FR_CHECK(e == cudaSuccess, "launch of ", kernelName(id), " failed: ", cudaGetErrorString(e));
   ++stats_.launches[(size_t)id];
+  if (cur_.launches == 0) cur_.first_kernel = (int32_t)id;
+  ++cur_.launches;
 }
 
 void Engine::runAllreduceSlice(Channel& ch, const CollectiveDesc& d, const void* in, void* out,
@@ -454,7 +470,33 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after,
   };
   const char* in = static_cast<const char*>(d.in);
   char* out = static_cast<char*>(d.out);
-  ++stats_.collectives;
+  const auto t_begin = std::chrono::steady_clock::now();
+  const uint64_t slices_before = stats_.slices;
+  cur_ = TraceEntry{};
+  cur_.seq = stats_.collectives;
+  cur_.kind = (int32_t)d.kind;
+  cur_.bytes = d.numel * wes * (d.kind == CollKind::ALLREDUCE ? 1 : W);
+  if (nvtx_) {
+    static const char* kNames[] = {"fairring.all_reduce", "fairring.reduce_scatter",
+                                   "fairring.all_gather"};
+    nvtxRangePushA(kNames[(int)d.kind]);
+  }
+  struct Finish {
+    Engine* e;
+    std::vector<int>* used;
+    std::chrono::steady_clock::time_point t0;
+    uint64_t slices0;
+    ~Finish() {
+      e->cur_.slices = (int32_t)(e->stats_.slices - slices0);
+      e->cur_.channels = (int32_t)used->size();
+      e->cur_.host_us =
+          std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
+      if (e->trace_.size() < kTraceLen) e->trace_.resize(kTraceLen);
+      e->trace_[e->cur_.seq % kTraceLen] = e->cur_;
+      ++e->stats_.collectives;
+      if (e->nvtx_) nvtxRangePop();
+    }
+  } finish{this, &used, t_begin, slices_before};
 
   if (runDirect(d, take) || runBounce(d, take)) {
     // nothing else to do

@@ -83,6 +83,18 @@ struct EngineStats {
   std::array<uint64_t, (size_t)KernelId::kCount> launches{};
 };
 
+// One line of the engine's trace: what a collective was turned into.
+struct TraceEntry {
+  uint64_t seq = 0;
+  int32_t kind = 0;           // CollKind
+  int64_t bytes = 0;          // wire bytes of the whole collective
+  int32_t first_kernel = -1;  // KernelId of the first launch
+  int32_t launches = 0;
+  int32_t slices = 0;
+  int32_t channels = 0;       // side streams used
+  double host_us = 0;         // time spent enqueueing
+};
+
 // FIFO of closures drained by one thread (fairring/utils.h:329-351 in the
 // reference).  Used when FAIRRING_COMMAND_THREAD=1.
 class CommandQueue {
@@ -131,6 +143,8 @@ class Engine {
   const MemoryPlan& plan() const { return plan_; }
   const EngineConfig& config() const { return cfg_; }
   EngineStats stats() const;
+  // The last collectives (newest last), at most 256.
+  std::vector<TraceEntry> trace() const;
   bool nvlsAvailable() const { return region_.mc_ptr != nullptr; }
   std::string describe() const;
   Algo chooseAllreduce(int64_t wire_bytes, DType wire, RedOp op) const;
@@ -170,6 +184,9 @@ class Engine {
   uint64_t next_channel_ = 0;
   std::mutex mu_;
   EngineStats stats_;
+  std::vector<TraceEntry> trace_;  // ring of kTraceLen entries
+  TraceEntry cur_;
+  bool nvtx_ = false;
   bool poisoned_ = false;
   int reset_count_ = 0;
 

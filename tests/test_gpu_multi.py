@@ -164,6 +164,9 @@ def _suite(rank, world, check_ddp):
         report["ddp"] = "ok"
 
     be.check_health()
+    tr = be.trace()
+    assert tr and int(tr[-1]["seq"]) == be.stats()["gpu_collectives"] - 1
+    assert all(int(t["launches"]) >= 1 for t in tr if int(t["bytes"]) > 0)
     report["stats"] = be.stats()
     report["describe"] = be.describe()
     dist.destroy_process_group()
@@ -180,6 +183,7 @@ CONFIGS = {
     "hier_three_kernels": {"FAIRRING_ALGO": "hier", "FAIRRING_NVLS": "off"},
     "ipc_transport_cmd_thread": {"FAIRRING_TRANSPORT": "ipc", "FAIRRING_COMMAND_THREAD": "1"},
     "machines_of_one_gpu": {"FAIRRING_GPUS_PER_MACHINE": "1", "FAIRRING_NVLS": "off"},
+    "machines_of_two_gpus": {"FAIRRING_GPUS_PER_MACHINE": "2", "FAIRRING_RANK_LAYOUT": "favorable"},
 }
 
 
@@ -204,6 +208,8 @@ def test_backend_on_gpus(name):
         assert stats["gpu_bounce_slices"] > 0
     if name == "hier_three_kernels":
         assert stats["launch_rs_intragroup"] > 0 and stats["launch_ag_intragroup"] > 0
+    if name == "machines_of_two_gpus" and world >= 4:
+        assert stats["launch_shard_server_reduce"] > 0 and stats["launch_rs_intragroup"] > 0
     if name == "machines_of_one_gpu":
         assert stats["launch_shard_server_reduce"] > 0
 
@@ -216,3 +222,65 @@ def test_groupings_on_8_gpus(gpm, layout):
            "FAIRRING_TOTAL_MEMORY": str(64 << 20), "FAIRRING_DEVICE_TIMEOUT_MS": "20000"}
     res = run_ranks(_suite, 8, env=env, args=(False,), timeout=900)
     assert res[0]["stats"]["launch_shard_server_reduce"] > 0
+
+
+# --- a rank stays away from one collective: time-out, report, reset, carry on -----
+def _absent_rank(rank, world):
+    """Host-made failure, no GPU fault: rank 1 simply does not call one
+    all_reduce.  Rank 0's kernel waits for its limit (1 s), records whom it was
+    waiting for and returns; the blocking wait raises; both ranks learn of it
+    through the store, reset the engine together and the next all_reduce works."""
+    import time
+    from datetime import timedelta
+
+    import torch.distributed as dist
+
+    import fairring
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("fairring", rank=rank, world_size=world, timeout=timedelta(seconds=60))
+    be = fairring.get_backend(device="cuda")
+    store = dist.distributed_c10d._get_default_store()
+    x = torch.ones(1 << 20, device=dev)
+    dist.all_reduce(x)  # healthy
+    torch.cuda.synchronize()
+    assert float(x[0]) == world
+    outcome = "n/a"
+    if rank == 0:
+        y = torch.ones(1 << 20, device=dev)
+        t0 = time.time()
+        try:
+            dist.all_reduce(y)  # FAIRRING_BLOCKING_WAIT=1: wait() watches the kernel
+            outcome = "completed"
+        except RuntimeError as e:
+            outcome = str(e)
+        elapsed = time.time() - t0
+        store.set("rank0_outcome", "done")
+    else:
+        store.wait(["rank0_outcome"])  # never joined the second collective
+        elapsed = 0.0
+    # the GPU is still fine
+    z = torch.arange(10, device=dev).sum().item()
+    assert z == 45
+    err_before = str(be.get_error()) if hasattr(be, "get_error") else ""
+    be.reset()
+    w = torch.full((1 << 20,), float(rank + 1), device=dev)
+    dist.all_reduce(w)
+    torch.cuda.synchronize()
+    after = float(w[0])
+    dist.destroy_process_group()
+    return outcome, elapsed, after
+
+
+def test_absent_rank_times_out_and_engine_recovers():
+    if _ngpu() < 2:
+        pytest.skip("needs at least two GPUs")
+    env = {"FAIRRING_NVLS": "off", "FAIRRING_DEVICE_TIMEOUT_MS": "1000", "FAIRRING_BLOCKING_WAIT": "1",
+           "FAIRRING_TOTAL_MEMORY": str(64 << 20), "NCCL_NVLS_ENABLE": "0"}
+    res = run_ranks(_absent_rank, 2, env=env, timeout=180)
+    outcome, elapsed, after = res[0]
+    assert "failed state" in outcome or "timed out" in outcome, outcome
+    assert "rank 1" in outcome
+    assert elapsed < 20
+    assert res[0][2] == 3.0 and res[1][2] == 3.0
