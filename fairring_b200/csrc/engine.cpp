@@ -239,6 +239,9 @@ void Engine::reset() {
   FR_CUDA(cudaDeviceSynchronize());
   std::memset(status_host_, 0, ((size_t)plan_.channels * kStatusWords + 16) * sizeof(uint32_t));
   poisoned_ = false;
+  // Ranks may have issued different numbers of collectives before the failure:
+  // start the round-robin over channels from the same place everywhere.
+  next_channel_ = 0;
   store_->barrier(pfx + "/clean", topo_.world, cfg_.bootstrap_timeout);
 }
 
