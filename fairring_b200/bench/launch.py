@@ -25,7 +25,9 @@ from datetime import timedelta
 
 def run_one_device(conn, args, machine_idx: int, device_idx: int) -> None:
     try:
-        os.environ["CUDA_VISIBLE_DEVICES"] = str(device_idx)
+        # Every child sees all GPUs and selects its own: peer mappings between
+        # processes need the peers' devices to be visible.  (The reference hides
+        # the others with CUDA_VISIBLE_DEVICES, launch_benchmark.py:51.)
         for k in ("NCCL_SOCKET_NTHREADS", "NCCL_NSOCKS_PERTHREAD"):
             v = getattr(args, k.lower())
             if v is not None:
@@ -48,7 +50,7 @@ def run_one_device(conn, args, machine_idx: int, device_idx: int) -> None:
         rank = machine_idx * args.num_devices_per_machine + device_idx
         rdv = dist.rendezvous(args.init_method, rank, world)
         store, _, _ = next(rdv)
-        torch.cuda.set_device(0)
+        torch.cuda.set_device(device_idx)
         timeout = timedelta(seconds=args.timeout)
         if args.use_nccl:
             opts = dist.ProcessGroupNCCL.Options()
@@ -59,7 +61,7 @@ def run_one_device(conn, args, machine_idx: int, device_idx: int) -> None:
         dtype = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[args.dtype]
         client = _C.BenchClient(backend, args.num_buckets, args.bucket_size, dtype,
                                 args.num_epochs, args.warmup_epochs, args.gaussian,
-                                not args.no_check, 0)
+                                not args.no_check, device_idx)
         stats = client.run()
         desc = "" if args.use_nccl else backend.describe()
         if not args.use_nccl:
