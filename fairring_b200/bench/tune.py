@@ -88,6 +88,7 @@ def main(argv=None) -> int:
         os.environ["FAIRRING_ALGO"] = {"twoshot": "twoshot", "nvls": "nvls", "bounce": "bounce"}.get(variant, "auto")
         os.environ["FAIRRING_DIRECT"] = {"sym_p2p": "p2p", "sym_nvls": "nvls"}.get(variant, "off")
         os.environ["FAIRRING_ONESHOT_MAX"] = "0"
+        os.environ["FAIRRING_BOUNCE"] = "on" if variant == "bounce" else "off"
         g = dist.new_group(backend="fairring")
         be = fairring_b200.get_backend(g, "cuda")
         buf = arena

@@ -819,6 +819,16 @@ at::Tensor BackendFairring::symmetricEmpty(int64_t numel, at::ScalarType dtype) 
                        at::TensorOptions().dtype(dtype).device(at::kCUDA, (c10::DeviceIndex)device));
 }
 
+bool BackendFairring::supportsTensorAlloc(c10::DeviceIndex) {
+  std::lock_guard<std::mutex> lk(mu_);
+  const Deployment& dep = ensureDeployment();
+  return dep.single_host && dep.topo.world <= kMaxRanks;
+}
+
+at::Tensor BackendFairring::allocateTensor(long size, at::TensorOptions options) {
+  return symmetricEmpty(size, c10::typeMetaToScalarType(options.dtype()));
+}
+
 void BackendFairring::skipCpuSignals(int n) {
   std::lock_guard<std::mutex> lk(mu_);
   ensureCpuEngine().skipSignals(n);

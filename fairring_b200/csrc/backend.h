@@ -54,7 +54,7 @@ struct OptionsFairring : c10d::Backend::Options {
   std::string nvls = "auto";       // auto | on | off
   std::string transport = "auto";  // auto | vmm | ipc
   std::string direct = "auto";     // auto | p2p | nvls | off: in-place path for symmetric tensors
-  std::string bounce = "auto";     // auto | on | off: copy-engine bounce buffers for big plain tensors
+  std::string bounce = "off";      // on | off: copy-engine bounce buffers for big plain tensors
   int64_t bounce_min_bytes = 64ll << 20;
   bool command_thread = false;
   bool blocking_wait = false;
@@ -171,6 +171,10 @@ class BackendFairring : public c10d::Backend {
   uint64_t getSequenceNumberForGroup() override { return seq_; }
   void setTimeout(std::chrono::milliseconds t) override { options_->timeout = t; }
   c10d::ErrorType getError() override;
+  // Communication-optimised memory: tensors from here are symmetric (peer- and
+  // multicast-mapped) and are all-reduced in place.
+  bool supportsTensorAlloc(c10::DeviceIndex device) override;
+  at::Tensor allocateTensor(long size, at::TensorOptions options = {}) override;
   void abort() override;
   void shutdown() override;
 

@@ -178,8 +178,8 @@ CONFIGS = {
     "twoshot_no_nvls": {"FAIRRING_NVLS": "off", "FAIRRING_ALGO": "twoshot"},
     "nvls": {"FAIRRING_ALGO": "nvls"},
     "nvls_oneshot": {"FAIRRING_ALGO": "nvls_oneshot"},
-    "bounce": {"FAIRRING_ALGO": "bounce"},
-    "bounce_p2p": {"FAIRRING_ALGO": "bounce", "FAIRRING_NVLS": "off"},
+    "bounce": {"FAIRRING_ALGO": "bounce", "FAIRRING_BOUNCE": "on"},
+    "bounce_p2p": {"FAIRRING_ALGO": "bounce", "FAIRRING_BOUNCE": "on", "FAIRRING_NVLS": "off"},
     "hier_three_kernels": {"FAIRRING_ALGO": "hier", "FAIRRING_NVLS": "off"},
     "ipc_transport_cmd_thread": {"FAIRRING_TRANSPORT": "ipc", "FAIRRING_COMMAND_THREAD": "1"},
     "machines_of_one_gpu": {"FAIRRING_GPUS_PER_MACHINE": "1", "FAIRRING_NVLS": "off"},
