@@ -45,6 +45,9 @@ def parse_args():
     ap.add_argument("--preset", choices=["flagship", "tiny"], default="flagship")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--bucket-mb", type=float, default=25.0)
+    ap.add_argument("--no-shadow", action="store_true",
+                    help="let autocast cast the fp32 weights on every forward instead of keeping "
+                         "a bf16 shadow copy written by the optimizer kernel")
     return ap.parse_args()
 
 
@@ -104,9 +107,11 @@ def main():
     lr, betas, wd = 1e-4, (0.9, 0.95), 0.1
 
     if args.impl == "fairring" and args.ddp == "flat":
-        ddp = FlatDataParallel(model, bucket_cap_mb=args.bucket_mb, wire_dtype=wire)
-        opt = FlatAdamW(ddp.flat_param, ddp.flat_grad, lr=lr, betas=betas, weight_decay=wd)
-        parallel_desc = "flat-dp"
+        ddp = FlatDataParallel(model, bucket_cap_mb=args.bucket_mb, wire_dtype=wire,
+                               bf16_shadow=not args.no_shadow)
+        opt = FlatAdamW(ddp.flat_param, ddp.flat_grad, lr=lr, betas=betas, weight_decay=wd,
+                        shadow=ddp.flat_shadow)
+        parallel_desc = "flat-dp" + ("" if args.no_shadow else " + bf16 shadow weights for autocast")
     else:
         from torch.nn.parallel import DistributedDataParallel as DDP
 

@@ -20,8 +20,12 @@ struct AdamWArgs {
 
 // p, g, m, v: fp32, 16-byte aligned, n elements each.  Decoupled weight decay,
 // same update as torch.optim.AdamW.
-cudaError_t launchAdamWFlat(float* p, const float* g, float* m, float* v, int64_t n,
-                            const AdamWArgs& a, int sm_count, cudaStream_t stream);
+// shadow_bf16 (may be null): receives a bf16 copy of the updated parameters.
+cudaError_t launchAdamWFlat(float* p, const float* g, float* m, float* v, void* shadow_bf16,
+                            int64_t n, const AdamWArgs& a, int sm_count, cudaStream_t stream);
+// dst (fp32, 16-byte aligned) = or += src (bf16, 16-byte aligned), n elements.
+cudaError_t launchBf16GradToF32(float* dst, const void* src_bf16, int64_t n, bool accumulate,
+                                int sm_count, cudaStream_t stream);
 // *out += sum(x^2); the caller zeroes *out.
 cudaError_t launchSumSq(const float* x, int64_t n, float* out, int sm_count, cudaStream_t stream);
 

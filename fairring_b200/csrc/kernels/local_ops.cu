@@ -3,6 +3,7 @@
 // the whole model instead of one per tensor) and a sum of squares for gradient
 // clipping.  Both are bandwidth-bound streaming kernels: 16-byte accesses,
 // grid-stride, one pass over the data.
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <atomic>
@@ -15,9 +16,11 @@ namespace {
 
 std::atomic<uint64_t> g_local_launches{0};
 
+template <bool kShadow>
 __global__ void __launch_bounds__(512)
 adamw_flat_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
-                  float* __restrict__ v, int64_t n, AdamWArgs a) {
+                  float* __restrict__ v, __nv_bfloat16* __restrict__ shadow, int64_t n,
+                  AdamWArgs a) {
   const int64_t n4 = n / 4;
   const float4* g4 = reinterpret_cast<const float4*>(g);
   float4* p4 = reinterpret_cast<float4*>(p);
@@ -41,10 +44,53 @@ adamw_flat_kernel(float* __restrict__ p, const float* __restrict__ g, float* __r
     p4[i] = pp;
     m4[i] = mm;
     v4[i] = vv;
+    if constexpr (kShadow) {
+      // bf16 copy of the new weights, for the layers that compute in bf16
+      __nv_bfloat162 lo = __floats2bfloat162_rn(pp.x, pp.y), hi = __floats2bfloat162_rn(pp.z, pp.w);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(shadow)[i] = packed;
+    }
   }
   // ragged tail (n not a multiple of 4)
   const int64_t tail = n4 * 4 + blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (tail < n) upd(p[tail], g[tail], m[tail], v[tail]);
+  if (tail < n) {
+    upd(p[tail], g[tail], m[tail], v[tail]);
+    if constexpr (kShadow) shadow[tail] = __float2bfloat16_rn(p[tail]);
+  }
+}
+
+// dst (fp32) = or += src (bf16): how bf16 weight gradients enter the flat fp32
+// gradient buffer.  8 elements per thread and step: one 16-byte load, two
+// 16-byte stores.
+__global__ void __launch_bounds__(512)
+bf16_grad_to_f32_kernel(float* __restrict__ dst, const __nv_bfloat16* __restrict__ src, int64_t n,
+                        int accumulate) {
+  const int64_t n8 = n / 8;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 raw = reinterpret_cast<const uint4*>(src)[i];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float4 a, b;
+    float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
+    float2 f2 = __bfloat1622float2(h[2]), f3 = __bfloat1622float2(h[3]);
+    a = make_float4(f0.x, f0.y, f1.x, f1.y);
+    b = make_float4(f2.x, f2.y, f3.x, f3.y);
+    float4* d = reinterpret_cast<float4*>(dst) + 2 * i;
+    if (accumulate) {
+      const float4 o0 = d[0], o1 = d[1];
+      a.x += o0.x; a.y += o0.y; a.z += o0.z; a.w += o0.w;
+      b.x += o1.x; b.y += o1.y; b.z += o1.z; b.w += o1.w;
+    }
+    d[0] = a;
+    d[1] = b;
+  }
+  const int64_t tail = n8 * 8 + blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (tail < n) {
+    const float x = __bfloat162float(src[tail]);
+    dst[tail] = accumulate ? dst[tail] + x : x;
+  }
 }
 
 __global__ void __launch_bounds__(512)
@@ -72,15 +118,20 @@ sumsq_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ out) {
 
 }  // namespace
 
-cudaError_t launchAdamWFlat(float* p, const float* g, float* m, float* v, int64_t n,
-                            const AdamWArgs& a, int sm_count, cudaStream_t stream) {
+cudaError_t launchAdamWFlat(float* p, const float* g, float* m, float* v, void* shadow_bf16,
+                            int64_t n, const AdamWArgs& a, int sm_count, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
   if (((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15u) return cudaErrorMisalignedAddress;
+  if (((uintptr_t)shadow_bf16) & 7u) return cudaErrorMisalignedAddress;
   int64_t blocks = (n / 4 + 511) / 512;
   const int64_t cap = (int64_t)sm_count * 4;  // 4 resident CTAs of 512 threads per SM
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  adamw_flat_kernel<<<(unsigned)blocks, 512, 0, stream>>>(p, g, m, v, n, a);
+  if (shadow_bf16 != nullptr)
+    adamw_flat_kernel<true><<<(unsigned)blocks, 512, 0, stream>>>(
+        p, g, m, v, static_cast<__nv_bfloat16*>(shadow_bf16), n, a);
+  else
+    adamw_flat_kernel<false><<<(unsigned)blocks, 512, 0, stream>>>(p, g, m, v, nullptr, n, a);
   g_local_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }
@@ -93,6 +144,20 @@ cudaError_t launchSumSq(const float* x, int64_t n, float* out, int sm_count, cud
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   sumsq_kernel<<<(unsigned)blocks, 512, 0, stream>>>(x, n, out);
+  g_local_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+cudaError_t launchBf16GradToF32(float* dst, const void* src_bf16, int64_t n, bool accumulate,
+                                int sm_count, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  if ((((uintptr_t)dst) & 15u) || (((uintptr_t)src_bf16) & 15u)) return cudaErrorMisalignedAddress;
+  int64_t blocks = (n / 8 + 511) / 512;
+  const int64_t cap = (int64_t)sm_count * 4;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  bf16_grad_to_f32_kernel<<<(unsigned)blocks, 512, 0, stream>>>(
+      dst, static_cast<const __nv_bfloat16*>(src_bf16), n, accumulate ? 1 : 0);
   g_local_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }

@@ -20,7 +20,8 @@ void checkFlat(const at::Tensor& t, const char* name) {
 
 // One AdamW step over flat buffers, in place.  `step` counts from 1.
 void adamwFlat(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, double lr, double beta1,
-               double beta2, double eps, double weight_decay, int64_t step, double grad_scale) {
+               double beta2, double eps, double weight_decay, int64_t step, double grad_scale,
+               c10::optional<at::Tensor> shadow) {
   checkFlat(p, "param");
   checkFlat(g, "grad");
   checkFlat(m, "exp_avg");
@@ -28,6 +29,13 @@ void adamwFlat(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, double lr
   TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(),
               "flat buffers must have the same length");
   TORCH_CHECK(step >= 1, "step counts from 1");
+  void* shadow_ptr = nullptr;
+  if (shadow.has_value() && shadow->defined()) {
+    TORCH_CHECK(shadow->is_cuda() && shadow->scalar_type() == at::kBFloat16 &&
+                    shadow->is_contiguous() && shadow->numel() == p.numel(),
+                "shadow must be a contiguous bf16 CUDA tensor as long as param");
+    shadow_ptr = shadow->data_ptr();
+  }
   c10::cuda::CUDAGuard guard(p.device());
   AdamWArgs a;
   a.lr = (float)lr;
@@ -40,9 +48,23 @@ void adamwFlat(at::Tensor p, at::Tensor g, at::Tensor m, at::Tensor v, double lr
   a.grad_scale = (float)grad_scale;
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   cudaError_t e = launchAdamWFlat(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(),
-                                  v.data_ptr<float>(), p.numel(), a, sms,
+                                  v.data_ptr<float>(), shadow_ptr, p.numel(), a, sms,
                                   c10::cuda::getCurrentCUDAStream());
   TORCH_CHECK(e == cudaSuccess, "adamw_flat launch failed: ", cudaGetErrorString(e));
+}
+
+// dst (fp32) = or += src (bf16); both contiguous, same length.
+void bf16GradToF32(at::Tensor dst, at::Tensor src, bool accumulate) {
+  TORCH_CHECK(dst.is_cuda() && dst.scalar_type() == at::kFloat && dst.is_contiguous(),
+              "dst must be a contiguous fp32 CUDA tensor");
+  TORCH_CHECK(src.is_cuda() && src.scalar_type() == at::kBFloat16 && src.is_contiguous() &&
+                  src.numel() == dst.numel(),
+              "src must be a contiguous bf16 CUDA tensor as long as dst");
+  c10::cuda::CUDAGuard guard(dst.device());
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  cudaError_t e = launchBf16GradToF32(dst.data_ptr<float>(), src.data_ptr(), dst.numel(), accumulate,
+                                      sms, c10::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "bf16_grad_to_f32 launch failed: ", cudaGetErrorString(e));
 }
 
 // Sum of squares of a flat fp32 buffer, as a 1-element device tensor.
@@ -64,7 +86,10 @@ void bindLocalOps(pybind11::module_& m) {
   namespace py = pybind11;
   m.def("adamw_flat_", &adamwFlat, py::arg("param"), py::arg("grad"), py::arg("exp_avg"),
         py::arg("exp_avg_sq"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"),
-        py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale") = 1.0);
+        py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale") = 1.0,
+        py::arg("shadow") = py::none());
+  m.def("bf16_grad_to_f32_", &bf16GradToF32, py::arg("dst"), py::arg("src"),
+        py::arg("accumulate") = false);
   m.def("sumsq", &sumSq, py::arg("x"));
 }
 

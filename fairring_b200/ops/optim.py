@@ -20,11 +20,14 @@ class FlatAdamW:
 
     def __init__(self, flat_param: torch.Tensor, flat_grad: torch.Tensor, lr: float = 1e-3,
                  betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8,
-                 weight_decay: float = 0.01):
+                 weight_decay: float = 0.01, shadow: torch.Tensor | None = None):
         if flat_param.shape != flat_grad.shape or flat_param.dim() != 1:
             raise ValueError("flat_param and flat_grad must be 1-D and equally long")
+        if shadow is not None and (shadow.shape != flat_param.shape or shadow.dtype != torch.bfloat16):
+            raise ValueError("shadow must be a bf16 tensor as long as flat_param")
         self.param = flat_param
         self.grad = flat_grad
+        self.shadow = shadow  # bf16 copy of the parameters, rewritten by every step
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.exp_avg = torch.zeros_like(flat_param)
         self.exp_avg_sq = torch.zeros_like(flat_param)
@@ -39,7 +42,7 @@ class FlatAdamW:
         self.step_count += 1
         _C.adamw_flat_(self.param, self.grad, self.exp_avg, self.exp_avg_sq, self.lr,
                        self.betas[0], self.betas[1], self.eps, self.weight_decay,
-                       self.step_count, grad_scale)
+                       self.step_count, grad_scale, self.shadow)
 
     def zero_grad(self, set_to_none: bool = True) -> None:  # noqa: ARG002
         """Gradients are overwritten by the next backward; nothing to do."""

@@ -57,11 +57,21 @@ class FlatDataParallel(nn.Module):
 
     ``bucket_cap_mb`` matches DDP's default of 25 MiB, the size the reference
     tunes its slices for (README.md:62).
+
+    ``bf16_shadow=True`` (for training under ``torch.autocast(bfloat16)``): the
+    weights and biases of ``nn.Linear`` layers are replaced by bf16 views into a
+    flat shadow buffer that the optimizer kernel rewrites from the fp32 master
+    weights every step.  Autocast then finds those weights already in bf16 (it
+    would cast them on every forward otherwise), and their bf16 gradients are
+    added into the fp32 flat gradient buffer by one small kernel each.  The
+    arithmetic is what autocast does anyway -- bf16 operands, fp32 master
+    weights, bf16 weight gradients widened to fp32 -- minus the cast kernels.
+    Use ``FlatAdamW(ddp.flat_param, ddp.flat_grad, shadow=ddp.flat_shadow)``.
     """
 
     def __init__(self, module: nn.Module, process_group=None, bucket_cap_mb: float = 25.0,
                  wire_dtype: Optional[torch.dtype] = None, broadcast_parameters: bool = True,
-                 symmetric_grads: bool = True):
+                 symmetric_grads: bool = True, bf16_shadow: bool = False):
         super().__init__()
         self.module = module
         self.process_group = process_group if process_group is not None else dist.group.WORLD
@@ -138,6 +148,27 @@ class FlatDataParallel(nn.Module):
                            if self.process_group is not dist.group.WORLD else 0,
                            group=self.process_group)
 
+        self.flat_shadow = None
+        from .. import _C
+
+        self._C = _C
+        if bf16_shadow:
+            self.flat_shadow = self.flat_param.to(torch.bfloat16)
+            for mod in module.modules():
+                if not isinstance(mod, nn.Linear):
+                    continue
+                for name in ("weight", "bias"):
+                    master = mod._parameters.get(name)
+                    if master is None or id(master) not in self._off_of:
+                        continue
+                    off = self._off_of[id(master)]
+                    view = self.flat_shadow[off:off + master.numel()].view_as(master)
+                    shadow = nn.Parameter(view, requires_grad=True)
+                    mod._parameters[name] = shadow
+                    self._off_of[id(shadow)] = off
+                    self._bucket_of[id(shadow)] = self._bucket_of[id(master)]
+                    shadow.register_post_accumulate_grad_hook(self._on_grad)
+
     # -- public ------------------------------------------------------------
     @property
     def num_buckets(self) -> int:
@@ -168,10 +199,13 @@ class FlatDataParallel(nn.Module):
     def _on_grad(self, p: torch.Tensor) -> None:
         off = self._off_of[id(p)]
         dst = self.flat_grad[off:off + p.numel()].view_as(p)
-        if self._accumulate:
-            dst.add_(p.grad)
+        g = p.grad
+        if g.dtype == torch.bfloat16 and g.is_contiguous() and g.data_ptr() % 16 == 0:
+            self._C.bf16_grad_to_f32_(dst.view(-1), g.view(-1), self._accumulate)
+        elif self._accumulate:
+            dst.add_(g)
         else:
-            dst.copy_(p.grad)
+            dst.copy_(g)
         p.grad = None  # the flat buffer is the gradient; views are handed out by grads()
         if not self._callback_queued:
             torch.autograd.Variable._execution_engine.queue_callback(self._finish_backward)

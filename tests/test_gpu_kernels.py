@@ -248,6 +248,71 @@ def test_fused_adamw_matches_torch(C):
     torch.testing.assert_close(C.sumsq(g), (g.double() ** 2).sum().float().reshape(1), rtol=1e-4, atol=0)
 
 
+def test_adamw_shadow_and_bf16_grad_kernel(C):
+    _need_gpu()
+    torch.manual_seed(1)
+    n = 300_007
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    p2, m2, v2 = p.clone(), m.clone(), v.clone()
+    shadow = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    C.adamw_flat_(p, g, m, v, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, shadow)
+    C.adamw_flat_(p2, g, m2, v2, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, 1.0)
+    assert torch.equal(p, p2) and torch.equal(shadow, p.to(torch.bfloat16))
+    for k in (8, 1000, 100_003):
+        src = torch.randn(k, device="cuda").to(torch.bfloat16)
+        dst = torch.full((k,), 2.0, device="cuda")
+        C.bf16_grad_to_f32_(dst, src, False)
+        assert torch.equal(dst, src.float())
+        C.bf16_grad_to_f32_(dst, src, True)
+        assert torch.equal(dst, src.float() * 2)
+
+
+def test_flat_data_parallel_bf16_shadow_matches_autocast(C):
+    """One rank: the shadow-weight path gives the gradients autocast gives."""
+    _need_gpu()
+    import os
+    import socket
+
+    import torch.distributed as dist
+
+    import fairring_b200  # noqa: F401
+    from fairring_b200.models import DecoderConfig, DecoderLM
+    from fairring_b200.ops import FlatAdamW
+    from fairring_b200.parallel import FlatDataParallel
+
+    if not dist.is_initialized():
+        s = socket.socket()
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+        s.close()
+        os.environ.setdefault("FAIRRING_TOTAL_MEMORY", str(64 << 20))
+        dist.init_process_group("fairring", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
+    cfg = DecoderConfig.tiny()
+    torch.manual_seed(0)
+    a = DecoderLM(cfg).cuda()
+    b = DecoderLM(cfg).cuda()
+    b.load_state_dict(a.state_dict())
+    tok = torch.randint(0, cfg.vocab, (4, cfg.seq_len + 1), device="cuda")
+    da = FlatDataParallel(a)
+    db = FlatDataParallel(b, bf16_shadow=True)
+    oa = FlatAdamW(da.flat_param, da.flat_grad, lr=1e-3)
+    ob = FlatAdamW(db.flat_param, db.flat_grad, lr=1e-3, shadow=db.flat_shadow)
+    for step in range(3):
+        losses = []
+        for d, o in ((da, oa), (db, ob)):
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = d(tok[:, :-1], tok[:, 1:])
+            loss.backward()
+            o.step()
+            losses.append(loss.item())
+        assert abs(losses[0] - losses[1]) < 2e-2, losses
+        torch.testing.assert_close(da.flat_grad, db.flat_grad, rtol=5e-2, atol=2e-3)
+    torch.testing.assert_close(db.flat_shadow.float(), db.flat_param, rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(da.flat_param, db.flat_param, rtol=1e-2, atol=2e-3)
+
+
 def test_launch_counter_counts(C):
     _need_gpu()
     before = C.launch_count()
