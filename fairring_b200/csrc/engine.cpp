@@ -289,7 +289,9 @@ bool Engine::runDirect(const CollectiveDesc& d, const std::function<Channel&()>&
   // 128 MiB: 757 GB/s with 2 channels, 743 with 4, 673 with 8).
   int64_t nslices = (int64_t)bytes / cfg_.direct_min_slice_bytes;
   if (nslices > (int64_t)channels_.size()) nslices = (int64_t)channels_.size();
-  if (nslices > cfg_.direct_max_slices) nslices = cfg_.direct_max_slices;
+  // ... while the peer-load variant keeps gaining up to 64 blocks (2 GPUs at
+  // 128 MiB: 456 GB/s with 2 channels of 16 blocks, 582 with 4).
+  if (nvls && nslices > cfg_.direct_max_slices) nslices = cfg_.direct_max_slices;
   if (nslices < 1) nslices = 1;
   const int64_t slice_elems = roundUp(ceilDiv(d.numel, nslices), V * W);
   for (int64_t start = 0; start < d.numel; start += slice_elems) {
