@@ -35,10 +35,10 @@ FAIRRING_NVLS_ONESHOT_MAX      largest message (bytes) for the NVLS one-shot ker
 FAIRRING_TRANSPORT             auto | vmm | ipc  (how peer memory is shared)
 FAIRRING_DIRECT                auto | nvls | p2p | off  (in-place kernels for tensors from
                                ``symmetric_empty``: no staging copies)
-FAIRRING_BOUNCE                on | off (default off): big ordinary tensors are moved by the
-                               copy engines through a symmetric bounce buffer that is reduced
-                               in place; takes a third of the memory budget
-FAIRRING_BOUNCE_MIN            smallest message (bytes) for the bounce path (default 64 MiB)
+FAIRRING_BOUNCE                auto | on | off: big ordinary tensors are copied by a wide kernel
+                               into a symmetric bounce buffer, reduced there in place and
+                               copied back; takes a third of the memory budget
+FAIRRING_BOUNCE_MIN            smallest message (bytes) for the bounce path (default 32 MiB)
 FAIRRING_DEVICE_TIMEOUT_MS     limit of one device-side wait on a peer (default 30000)
 FAIRRING_COMMAND_THREAD        1: enqueue kernels from a dedicated thread
 FAIRRING_BLOCKING_WAIT         1: Work.wait() blocks the host and reports kernel failures
@@ -120,7 +120,7 @@ def options_from_env(timeout: timedelta | None = None) -> "_C.Options":
     opts.nvls = os.environ.get("FAIRRING_NVLS", "auto").lower()
     opts.transport = os.environ.get("FAIRRING_TRANSPORT", "auto").lower()
     opts.direct = os.environ.get("FAIRRING_DIRECT", "auto").lower()
-    opts.bounce = os.environ.get("FAIRRING_BOUNCE", "off").lower()
+    opts.bounce = os.environ.get("FAIRRING_BOUNCE", "auto").lower()
     opts.bounce_min_bytes = _env_int("FAIRRING_BOUNCE_MIN", opts.bounce_min_bytes)
     opts.command_thread = os.environ.get("FAIRRING_COMMAND_THREAD", "0") == "1"
     opts.blocking_wait = os.environ.get("FAIRRING_BLOCKING_WAIT", "0") == "1"

@@ -54,8 +54,8 @@ struct OptionsFairring : c10d::Backend::Options {
   std::string nvls = "auto";       // auto | on | off
   std::string transport = "auto";  // auto | vmm | ipc
   std::string direct = "auto";     // auto | p2p | nvls | off: in-place path for symmetric tensors
-  std::string bounce = "off";      // on | off: copy-engine bounce buffers for big plain tensors
-  int64_t bounce_min_bytes = 64ll << 20;
+  std::string bounce = "auto";     // auto | on | off: symmetric bounce buffers for big plain tensors
+  int64_t bounce_min_bytes = 32ll << 20;
   bool command_thread = false;
   bool blocking_wait = false;
   std::string boot_id_override;    // tests: pretend to be on another host

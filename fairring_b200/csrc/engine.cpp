@@ -9,6 +9,7 @@
 #include <cstdlib>
 
 #include "check.h"
+#include "kernels/local_kernels.h"
 
 namespace fairring {
 
@@ -79,7 +80,7 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
   const int budget = std::max(cfg_.blocks, std::min(sms, cfg_.sm_budget));
   const int max_channels = std::max(1, budget / cfg_.blocks);
   if (cfg_.parallelism > max_channels) cfg_.parallelism = max_channels;
-  const bool want_bounce = cfg_.bounce == "on" && topo_.world > 1 && topo_.M == 1;
+  const bool want_bounce = cfg_.bounce != "off" && topo_.world > 1 && topo_.M == 1;
   // With bounce buffers the budget is cut in three equal parts per channel:
   // the two staging halves and the bounce buffer.
   plan_ = planMemory(want_bounce ? cfg_.total_memory / 3 * 2 : cfg_.total_memory, cfg_.slice_bytes,
@@ -314,8 +315,10 @@ bool Engine::runDirect(const CollectiveDesc& d, const std::function<Channel&()>&
   return true;
 }
 
-// Ordinary tensor, big message: copy engine in -> in-place kernel on the
-// symmetric bounce buffer -> copy engine out, all on the channel's stream.  The
+// Ordinary tensor, big message: copy kernel in -> in-place kernel on the
+// symmetric bounce buffer -> copy kernel out, all on the channel's stream.  The
+// copy kernels do not wait on anybody, so they may be wide without touching
+// the residency bound.  The
 // kernel's closing barrier means every peer is done with this rank's buffer
 // before the copy-out (and the next copy-in) touches it, so one buffer per
 // channel is enough.
@@ -344,8 +347,7 @@ bool Engine::runBounce(const CollectiveDesc& d, const std::function<Channel&()>&
     Channel& ch = take();
     const size_t o = (size_t)(&ch - channels_.data()) * (size_t)plan_.half_bytes;
     char* mine = static_cast<char*>(bounce_.ptrs[topo_.rank]) + o;
-    FR_CUDA(cudaMemcpyAsync(mine, in + start * es, (size_t)n * es, cudaMemcpyDeviceToDevice,
-                            ch.stream));
+    FR_CUDA(launchCopy(mine, in + start * es, (size_t)n * es, cfg_.bounce_copy_blocks, ch.stream));
     OpArgs a{};
     a.seg = allreduceSeg(n, es, W);
     a.scale = 1.0f;
@@ -356,8 +358,7 @@ bool Engine::runBounce(const CollectiveDesc& d, const std::function<Channel&()>&
     a.mc = nvls ? static_cast<char*>(bounce_.mc_ptr) + o : nullptr;
     a.in[0] = a.out[0] = mine;
     launch(ch, nvls ? KernelId::NVLS_DIRECT : KernelId::P2P_DIRECT, a);
-    FR_CUDA(cudaMemcpyAsync(out + start * es, mine, (size_t)n * es, cudaMemcpyDeviceToDevice,
-                            ch.stream));
+    FR_CUDA(launchCopy(out + start * es, mine, (size_t)n * es, cfg_.bounce_copy_blocks, ch.stream));
     ++stats_.slices;
     ++stats_.bounce_slices;
   }

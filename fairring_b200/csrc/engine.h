@@ -54,14 +54,13 @@ struct EngineConfig {
   std::string direct = "auto";
   int64_t direct_min_slice_bytes = 2ll << 20;  // a message is split over channels down to this
   int32_t direct_max_slices = 2;               // ... but an in-place message into at most this many
-  // Ordinary (non-symmetric) tensors of at least bounce_min_bytes can be moved
-  // into and out of a symmetric bounce buffer by the copy engines and reduced
-  // there in place: the SMs only run the in-place kernel.  "on" | "off".
-  // A third of the memory budget becomes bounce buffers when this is enabled.
-  // Off by default: on 8 GPUs it measured 470-506 GB/s against 484-512 GB/s for
-  // the fused staged kernels, and each copy costs ~7 us of host time.
-  std::string bounce = "off";
-  int64_t bounce_min_bytes = 64ll << 20;
+  // Ordinary (non-symmetric) tensors of at least bounce_min_bytes are copied by
+  // a wide kernel into a symmetric bounce buffer, reduced there in place by the
+  // zero-copy kernel and copied back.  "auto" | "on" | "off".  A third of the
+  // memory budget becomes bounce buffers when this is enabled.
+  std::string bounce = "auto";
+  int32_t bounce_copy_blocks = 96;
+  int64_t bounce_min_bytes = 32ll << 20;
   std::chrono::milliseconds bootstrap_timeout{120000};
 };
 

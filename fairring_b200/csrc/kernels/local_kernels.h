@@ -29,6 +29,10 @@ cudaError_t launchBf16GradToF32(float* dst, const void* src_bf16, int64_t n, boo
 // *out += sum(x^2); the caller zeroes *out.
 cudaError_t launchSumSq(const float* x, int64_t n, float* out, int sm_count, cudaStream_t stream);
 
+// Device-to-device copy by a kernel of at most `blocks` blocks (falls back to
+// cudaMemcpyAsync when a pointer is not 16-byte aligned).
+cudaError_t launchCopy(void* dst, const void* src, size_t bytes, int blocks, cudaStream_t stream);
+
 uint64_t localLaunchCountImpl();
 
 }  // namespace fairring
