@@ -233,3 +233,62 @@ def test_ranks_on_different_hosts_are_delegated():
         np.testing.assert_array_equal(t, np.full(10, 3.0))
         assert dep["num_hosts"] == 2 and dep["single_host"] == 0
         assert stats["delegated"] >= 1 and "cpu_collectives" not in stats
+
+
+# --- torch DDP on CPU tensors through this backend (Future plumbing, parity with gloo) ----
+def _w_ddp_cpu(rank, world):
+    import torch.nn as nn
+    from torch.nn.parallel import DistributedDataParallel as DDP
+
+    dist = _init(rank, world)
+    gloo = dist.new_group(backend="gloo")
+    torch.manual_seed(0)
+    base = nn.Sequential(nn.Linear(32, 64), nn.Tanh(), nn.Linear(64, 8))
+    state = {k: v.clone() for k, v in base.state_dict().items()}
+    x = torch.randn(16, 32, generator=torch.Generator().manual_seed(rank))
+
+    def grads(pg):
+        m = nn.Sequential(nn.Linear(32, 64), nn.Tanh(), nn.Linear(64, 8))
+        m.load_state_dict(state)
+        d = DDP(m, process_group=pg, bucket_cap_mb=0.001)
+        d(x).pow(2).sum().backward()
+        return [p.grad.clone() for p in m.parameters()]
+
+    mine, ref = grads(None), grads(gloo)
+    work = dist.all_reduce(torch.ones(10), async_op=True)
+    fut = work.get_future()
+    fut.wait()
+    ok = work.is_completed() and work.is_success()
+    dist.destroy_process_group()
+    return [g.numpy() for g in mine], [g.numpy() for g in ref], ok
+
+
+def test_torch_ddp_on_cpu_matches_gloo():
+    res = run_ranks(_w_ddp_cpu, 2)
+    for mine, ref, ok in res:
+        assert ok
+        for a, b in zip(mine, ref):
+            np.testing.assert_allclose(a, b, rtol=1e-5, atol=1e-6)
+    for a, b in zip(res[0][0], res[1][0]):
+        np.testing.assert_array_equal(a, b)
+
+
+def test_options_from_env(monkeypatch):
+    import fairring_b200
+
+    monkeypatch.setenv("FAIRRING_TOTAL_MEMORY", "1234567")
+    monkeypatch.setenv("FAIRRING_SLICE_SIZE", "4194304")
+    monkeypatch.setenv("FAIRRING_PARALLELISM", "3")
+    monkeypatch.setenv("FAIRRING_GPUS_PER_MACHINE", "4")
+    monkeypatch.setenv("FAIRRING_RANK_LAYOUT", "favorable")
+    monkeypatch.setenv("FAIRRING_ALGO", "HIER")
+    o = fairring_b200.options_from_env()
+    assert o.max_memory_allocated_in_bytes == 1234567 and o.slice_size_in_bytes == 4194304
+    assert o.min_parallelism == 3 and o.gpus_per_machine == 4 and o.favorable_layout
+    assert o.algo == "hier" and o.is_high_priority_stream
+    monkeypatch.delenv("FAIRRING_TOTAL_MEMORY")
+    o = fairring_b200.options_from_env()
+    assert o.max_memory_allocated_in_bytes == 50 * 1024 * 1024  # the reference's default
+    monkeypatch.setenv("FAIRRING_RANK_LAYOUT", "sideways")
+    with pytest.raises(ValueError):
+        fairring_b200.options_from_env()
