@@ -30,6 +30,7 @@ SOURCES = [
     "emulate.cpp",
     "bench_client.cpp",
     "local_ops.cpp",
+    "selftest.cpp",
     "kernels/collectives.cu",
     "kernels/collectives_u8.cu",
     "kernels/collectives_i8.cu",

@@ -34,6 +34,7 @@ void segvHandler(int sig) {
 }  // namespace
 
 namespace fairring {
+void bindSelfTest(pybind11::module_& m);
 std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
     const std::string& kind, std::vector<at::Tensor> inputs, int64_t gpus_per_machine,
     bool favorable, const std::string& op, double scale, c10::optional<at::ScalarType> wire_dtype,
@@ -201,4 +202,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("VEC_BYTES") = kVecBytes;
 
   bindLocalOps(m);
+  bindSelfTest(m);
 }

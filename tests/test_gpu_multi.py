@@ -214,7 +214,7 @@ def test_backend_on_gpus(name):
         assert stats["launch_shard_server_reduce"] > 0
 
 
-@pytest.mark.parametrize("gpm,layout", [(2, "standard"), (2, "favorable"), (4, "standard"), (1, "favorable")])
+@pytest.mark.parametrize("gpm,layout", [(2, "favorable"), (4, "standard")])
 def test_groupings_on_8_gpus(gpm, layout):
     if _ngpu() < 8:
         pytest.skip("needs eight GPUs")
