@@ -292,3 +292,26 @@ def test_options_from_env(monkeypatch):
     monkeypatch.setenv("FAIRRING_RANK_LAYOUT", "sideways")
     with pytest.raises(ValueError):
         fairring_b200.options_from_env()
+
+
+# --- the process group can be torn down and built again in the same processes ----------
+def _w_reinit(rank, world):
+    import torch.distributed as dist
+
+    import fairring  # noqa: F401
+
+    out = []
+    for generation in range(3):
+        dist.init_process_group("fairring", rank=rank, world_size=world)
+        t = torch.full((50_000,), float(rank + generation))
+        dist.all_reduce(t)
+        out.append(float(t[0]))
+        dist.barrier()
+        dist.destroy_process_group()
+    return out
+
+
+def test_process_group_can_be_rebuilt():
+    res = run_ranks(_w_reinit, 2)
+    for r in res:
+        assert r == [1.0, 3.0, 5.0]
