@@ -13,6 +13,7 @@
 #include <thread>
 
 #include "cpu_path.h"
+#include "engine.h"
 #include "kvstore.h"
 
 namespace fairring {
@@ -119,12 +120,44 @@ int64_t cpuSelfTest(int world, int gpus_per_machine, bool favorable, std::vector
   return total;
 }
 
+// Several producer threads push numbered closures; one consumer drains the
+// queue as the engine's command thread does.  Returns the number of violations
+// of "every item runs exactly once, and items of one producer run in order".
+int64_t commandQueueSelfTest(int producers, int items_per_producer) {
+  CommandQueue q;
+  std::vector<std::vector<int>> seen(producers);
+  std::thread consumer([&] {
+    for (;;) {
+      auto fn = q.pop();
+      if (!fn) break;
+      fn();
+    }
+  });
+  std::vector<std::thread> ps;
+  for (int p = 0; p < producers; ++p)
+    ps.emplace_back([&, p] {
+      for (int i = 0; i < items_per_producer; ++i) q.push([&seen, p, i] { seen[p].push_back(i); });
+    });
+  for (auto& t : ps) t.join();
+  q.push(std::function<void()>());
+  consumer.join();
+  int64_t bad = 0;
+  for (int p = 0; p < producers; ++p) {
+    if ((int)seen[p].size() != items_per_producer) ++bad;
+    for (size_t i = 0; i < seen[p].size(); ++i)
+      if (seen[p][i] != (int)i) ++bad;
+  }
+  return bad;
+}
+
 void bindSelfTest(pybind11::module_& m) {
   namespace py = pybind11;
   m.def("cpu_self_test", &cpuSelfTest, py::arg("world"), py::arg("gpus_per_machine"),
         py::arg("favorable"), py::arg("numels"), py::arg("total_memory") = 1 << 20,
         py::arg("slice_bytes") = 0, py::arg("oneshot_max") = 1024, py::arg("use_max") = false,
         py::call_guard<py::gil_scoped_release>());
+  m.def("command_queue_self_test", &commandQueueSelfTest, py::arg("producers") = 4,
+        py::arg("items_per_producer") = 10000, py::call_guard<py::gil_scoped_release>());
 }
 
 }  // namespace fairring

@@ -51,3 +51,8 @@ def test_property_random_shapes(C):
                                oneshot_max=oneshot, use_max=use_max) == 0
 
     run()
+
+
+def test_command_queue_is_fifo_per_producer_and_loses_nothing(C):
+    assert C.command_queue_self_test(1, 1000) == 0
+    assert C.command_queue_self_test(8, 20000) == 0
