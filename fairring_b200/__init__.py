@@ -22,7 +22,7 @@ FAIRRING_PARALLELISM           slices in flight = side streams/channels (default
 FAIRRING_SLICE_SIZE            max bytes per slice (default 25 MiB, DDP's bucket size)
 FAIRRING_GPUS_PER_MACHINE      D of the M x D grouping (default: all ranks of a host)
 FAIRRING_RANK_LAYOUT           "standard" (rank = m*D+d) or "favorable" (rank = d*M+m)
-FAIRRING_ALGO                  auto | oneshot | twoshot | hier | nvls | nvls_oneshot | bounce
+FAIRRING_ALGO                  auto | oneshot | twoshot | hier | nvls | nvls_oneshot | pipe
 FAIRRING_BLOCKS                thread blocks per kernel (default 16, max 64)
 FAIRRING_SM_BUDGET             SMs the collectives may occupy at once (default 64): the number
                                of channels is at most SM_BUDGET / BLOCKS.  Raise it (up to the
@@ -35,11 +35,21 @@ FAIRRING_NVLS_ONESHOT_MAX      largest message (bytes) for the NVLS one-shot ker
 FAIRRING_TRANSPORT             auto | vmm | ipc  (how peer memory is shared)
 FAIRRING_DIRECT                auto | nvls | p2p | off  (in-place kernels for tensors from
                                ``symmetric_empty``: no staging copies)
-FAIRRING_BOUNCE                auto | on | off: big ordinary tensors are copied by a wide kernel
-                               into a symmetric bounce buffer, reduced there in place and
-                               copied back; takes a third of the memory budget
-FAIRRING_BOUNCE_MIN            smallest message (bytes) for the bounce path (default 32 MiB)
-FAIRRING_DEVICE_TIMEOUT_MS     limit of one device-side wait on a peer (default 30000)
+FAIRRING_PIPE                  auto | on | off: ordinary tensors of FAIRRING_PIPE_MIN bytes and more
+                               take the pipelined kernel (bulk copy in, switch reduce, bulk copy
+                               out, chunk by chunk in one launch); its staging rings take a third
+                               of the memory budget
+FAIRRING_PIPE_MIN              smallest message (bytes) for the pipelined kernel (default 512 KiB)
+FAIRRING_PIPE_BLOCKS           thread blocks of a pipelined launch (default 16)
+FAIRRING_PIPE_CHANNELS         rings, i.e. pipelined launches that may overlap (default 2)
+FAIRRING_PIPE_SLOTS            ring length in chunks (default 4)
+FAIRRING_PIPE_CHUNK            chunk bytes (default: from the message size)
+FAIRRING_PIPE_STAGE / _STAGES  shared-memory stage bytes / stages per copy role (16 KiB x 6)
+FAIRRING_DIRECT_MAX_SLICES     in-place NVLS messages are split over at most this many channels
+FAIRRING_DIRECT_MIN_SLICE      ... down to slices of this many bytes
+FAIRRING_DEVICE_TIMEOUT_MS     limit of one device-side wait on a peer (default: the process
+                               group's timeout; a wait that runs out leaves the tensor
+                               unreduced and poisons the engine until reset())
 FAIRRING_COMMAND_THREAD        1: enqueue kernels from a dedicated thread
 FAIRRING_BLOCKING_WAIT         1: Work.wait() blocks the host and reports kernel failures
 =============================  ==========================================================
@@ -120,8 +130,16 @@ def options_from_env(timeout: timedelta | None = None) -> "_C.Options":
     opts.nvls = os.environ.get("FAIRRING_NVLS", "auto").lower()
     opts.transport = os.environ.get("FAIRRING_TRANSPORT", "auto").lower()
     opts.direct = os.environ.get("FAIRRING_DIRECT", "auto").lower()
-    opts.bounce = os.environ.get("FAIRRING_BOUNCE", "auto").lower()
-    opts.bounce_min_bytes = _env_int("FAIRRING_BOUNCE_MIN", opts.bounce_min_bytes)
+    opts.pipe = os.environ.get("FAIRRING_PIPE", "auto").lower()
+    opts.pipe_min_bytes = _env_int("FAIRRING_PIPE_MIN", opts.pipe_min_bytes)
+    opts.pipe_blocks = _env_int("FAIRRING_PIPE_BLOCKS", opts.pipe_blocks)
+    opts.pipe_channels = _env_int("FAIRRING_PIPE_CHANNELS", opts.pipe_channels)
+    opts.pipe_slots = _env_int("FAIRRING_PIPE_SLOTS", opts.pipe_slots)
+    opts.pipe_chunk_bytes = _env_int("FAIRRING_PIPE_CHUNK", opts.pipe_chunk_bytes)
+    opts.pipe_stage_bytes = _env_int("FAIRRING_PIPE_STAGE", opts.pipe_stage_bytes)
+    opts.pipe_stages = _env_int("FAIRRING_PIPE_STAGES", opts.pipe_stages)
+    opts.direct_max_slices = _env_int("FAIRRING_DIRECT_MAX_SLICES", opts.direct_max_slices)
+    opts.direct_min_slice_bytes = _env_int("FAIRRING_DIRECT_MIN_SLICE", opts.direct_min_slice_bytes)
     opts.command_thread = os.environ.get("FAIRRING_COMMAND_THREAD", "0") == "1"
     opts.blocking_wait = os.environ.get("FAIRRING_BLOCKING_WAIT", "0") == "1"
     opts.boot_id_override = os.environ.get("FAIRRING_BOOT_ID", "")

@@ -77,6 +77,12 @@ WorkFairring::WorkFairring(c10d::OpType op, std::shared_ptr<Engine> engine, int 
   if (!engine_) enqueued_ = true;  // nothing to wait for (CPU path, world of one)
 }
 
+WorkFairring::~WorkFairring() {
+  // The completion event goes back to the engine only now: nobody can wait on
+  // this Work any more, so nobody can observe its next use.
+  if (engine_ && done_) engine_->releaseEvent(done_);
+}
+
 void WorkFairring::markEnqueued(cudaEvent_t done, cudaStream_t join) {
   {
     std::lock_guard<std::mutex> lk(mu_);
@@ -255,15 +261,25 @@ std::shared_ptr<Engine> BackendFairring::ensureEngine(int device) {
   cfg.oneshot_max_bytes = options_->oneshot_max_bytes;
   cfg.nvls_min_bytes = options_->nvls_min_bytes;
   cfg.nvls_oneshot_max_bytes = options_->nvls_oneshot_max_bytes;
-  cfg.device_timeout_ns = (uint64_t)options_->device_timeout_ms * 1000000ull;
+  const int64_t wait_ms = options_->device_timeout_ms > 0 ? options_->device_timeout_ms
+                                                          : (int64_t)options_->timeout.count();
+  cfg.device_timeout_ns = (uint64_t)std::max<int64_t>(wait_ms, 1) * 1000000ull;
   cfg.algo = parseAlgo(options_->algo);
   cfg.high_priority = options_->is_high_priority_stream;
   cfg.command_thread = options_->command_thread;
   cfg.transport = parseTransport(options_->transport);
   cfg.nvls = parseNvls(options_->nvls);
   cfg.direct = options_->direct;
-  cfg.bounce = options_->bounce;
-  cfg.bounce_min_bytes = options_->bounce_min_bytes;
+  cfg.pipe = options_->pipe;
+  cfg.pipe_min_bytes = options_->pipe_min_bytes;
+  cfg.pipe_blocks = (int32_t)options_->pipe_blocks;
+  cfg.pipe_channels = (int32_t)options_->pipe_channels;
+  cfg.pipe_slots = (int32_t)options_->pipe_slots;
+  cfg.pipe_chunk_bytes = options_->pipe_chunk_bytes;
+  cfg.pipe_stage_bytes = (int32_t)options_->pipe_stage_bytes;
+  cfg.pipe_stages = (int32_t)options_->pipe_stages;
+  cfg.direct_max_slices = (int32_t)options_->direct_max_slices;
+  cfg.direct_min_slice_bytes = options_->direct_min_slice_bytes;
   cfg.bootstrap_timeout = options_->timeout;
   c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
   engine_ = std::make_shared<Engine>(std::make_shared<StoreAdapter>(store_, "fairring/gpu/"),
@@ -281,7 +297,10 @@ CpuEngine& BackendFairring::ensureCpuEngine() {
                                  options_->slice_size_in_bytes, 1, dep.topo.world, 4096);
     cpu_engine_.reset(new CpuEngine(std::make_shared<StoreAdapter>(store_, "fairring/cpu/"),
                                     dep.topo, plan,
-                                    std::chrono::milliseconds(options_->device_timeout_ms)));
+                                    std::chrono::milliseconds(
+                                        options_->device_timeout_ms > 0
+                                            ? options_->device_timeout_ms
+                                            : (int64_t)options_->timeout.count())));
     cpu_engine_->oneshotMaxBytes = std::min<int64_t>(options_->oneshot_max_bytes, 32 << 10);
   }
   return *cpu_engine_;
@@ -356,7 +375,14 @@ c10::intrusive_ptr<c10d::Work> BackendFairring::runGpu(c10d::OpType type, const 
     try {
       c10::cuda::CUDAGuard g2(di);
       std::vector<cudaStream_t> used;
-      cudaStream_t s = engine->run(d, after, &used);
+      cudaStream_t s = nullptr;
+      try {
+        s = engine->run(d, after, &used);
+      } catch (...) {
+        engine->releaseEvent(after);
+        throw;
+      }
+      engine->releaseEvent(after);  // the side streams' waits on it are enqueued
       // The tensors are used on side streams: tell the caching allocator, as
       // the reference does for its stage streams (device.cc:297-301).
       for (const auto& t : keep)
@@ -727,7 +753,9 @@ std::map<std::string, int64_t> BackendFairring::stats() {
     m["gpu_collectives"] = (int64_t)s.collectives;
     m["gpu_slices"] = (int64_t)s.slices;
     m["gpu_wire_bytes"] = (int64_t)s.wire_bytes;
-    m["gpu_bounce_slices"] = (int64_t)s.bounce_slices;
+    m["symmetric_regions"] = (int64_t)s.symmetric_regions;
+    m["symmetric_bytes"] = (int64_t)s.symmetric_bytes;
+    m["symmetric_pending_release"] = (int64_t)s.symmetric_pending;
     for (int k = 0; k < (int)KernelId::kCount; ++k)
       m[std::string("launch_") + kernelName((KernelId)k)] = (int64_t)s.launches[k];
     m["nvls"] = engine_->nvlsAvailable() ? 1 : 0;
@@ -792,6 +820,31 @@ void BackendFairring::checkHealth() {
   }
 }
 
+std::string BackendFairring::health() {
+  std::shared_ptr<Engine> e;
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    e = engine_;
+  }
+  std::string what;
+  if (e && e->health(&what) != kStatusOk) return what.empty() ? "failed" : what;
+  return "";
+}
+
+int64_t BackendFairring::releaseSymmetric() {
+  std::shared_ptr<Engine> e;
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    e = engine_;
+  }
+  if (!e) return 0;
+  try {
+    return e->releaseFreedSymmetric();
+  } catch (const Error& err) {
+    TORCH_CHECK(false, err.what());
+  }
+}
+
 void BackendFairring::reset() {
   std::lock_guard<std::mutex> lk(mu_);
   if (engine_) engine_->reset();
@@ -812,10 +865,11 @@ at::Tensor BackendFairring::symmetricEmpty(int64_t numel, at::ScalarType dtype) 
   } catch (const Error& e) {
     TORCH_CHECK(false, e.what());
   }
-  // The memory belongs to the engine (it is unmapped when the process group
-  // goes away); the tensor only borrows it.
+  // When the tensor dies the region is marked free; it is unmapped at the next
+  // collective boundary at which every rank has let go of it (the next
+  // symmetric_empty or release_symmetric), or with the process group.
   auto keep = engine;
-  return at::from_blob(p, {numel}, [keep](void*) {},
+  return at::from_blob(p, {numel}, [keep](void* q) { keep->freeSymmetric(q); },
                        at::TensorOptions().dtype(dtype).device(at::kCUDA, (c10::DeviceIndex)device));
 }
 

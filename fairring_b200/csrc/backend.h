@@ -50,12 +50,23 @@ struct OptionsFairring : c10d::Backend::Options {
   int64_t oneshot_max_bytes = 256 << 10;
   int64_t nvls_min_bytes = 0;
   int64_t nvls_oneshot_max_bytes = 2 << 20;
-  int64_t device_timeout_ms = 30000;
+  // Limit of one device-side wait on a peer.  0: the process group's timeout,
+  // so that a rank that is merely late (checkpointing, evaluation, a data stall)
+  // is waited for as long as the other collectives of the group would wait.
+  int64_t device_timeout_ms = 0;
   std::string nvls = "auto";       // auto | on | off
   std::string transport = "auto";  // auto | vmm | ipc
   std::string direct = "auto";     // auto | p2p | nvls | off: in-place path for symmetric tensors
-  std::string bounce = "auto";     // auto | on | off: symmetric bounce buffers for big plain tensors
-  int64_t bounce_min_bytes = 32ll << 20;
+  std::string pipe = "auto";       // auto | on | off: pipelined kernel for ordinary tensors
+  int64_t pipe_min_bytes = 512 << 10;
+  int64_t pipe_blocks = 16;
+  int64_t pipe_channels = 2;
+  int64_t pipe_slots = 4;
+  int64_t pipe_chunk_bytes = 0;
+  int64_t pipe_stage_bytes = 16 << 10;
+  int64_t pipe_stages = 6;
+  int64_t direct_max_slices = 2;
+  int64_t direct_min_slice_bytes = 2 << 20;
   bool command_thread = false;
   bool blocking_wait = false;
   std::string boot_id_override;    // tests: pretend to be on another host
@@ -73,6 +84,7 @@ class WorkFairring : public c10d::Work {
   WorkFairring(c10d::OpType op, std::shared_ptr<Engine> engine, int device,
                std::vector<at::Tensor> result, bool blocking,
                std::chrono::milliseconds default_timeout);
+  ~WorkFairring() override;
   bool isCompleted() override;
   bool isSuccess() const override;
   std::exception_ptr exception() const override;
@@ -183,7 +195,12 @@ class BackendFairring : public c10d::Backend {
   std::string describe();
   std::map<std::string, int64_t> stats();
   void checkHealth();
+  // Host-side look at the kernels' status words, without synchronising: empty
+  // when healthy, else what gave up waiting for whom.
+  std::string health();
   void reset();
+  // Collective: unmap the symmetric tensors that have died on every rank.
+  int64_t releaseSymmetric();
   void skipCpuSignals(int n);
   // Collective: a 1-D tensor in symmetric memory of the current CUDA device;
   // all_reduce on (slices of) it runs in place without staging copies.

@@ -40,6 +40,10 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
     bool favorable, const std::string& op, double scale, c10::optional<at::ScalarType> wire_dtype,
     const std::string& algo, int64_t blocks, int64_t half_bytes, int64_t timeout_ms,
     int64_t silent_rank, int64_t repeats);
+std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedPipeAllreduce(
+    std::vector<at::Tensor> inputs, const std::string& op, double scale, int64_t blocks,
+    int64_t chunk_bytes, int64_t slot_bytes, int64_t slots, int64_t stage_bytes, int64_t stages,
+    int64_t timeout_ms, int64_t silent_rank, int64_t repeats);
 }
 
 template <typename T>
@@ -72,8 +76,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("nvls", &OptionsFairring::nvls)
       .def_readwrite("transport", &OptionsFairring::transport)
       .def_readwrite("direct", &OptionsFairring::direct)
-      .def_readwrite("bounce", &OptionsFairring::bounce)
-      .def_readwrite("bounce_min_bytes", &OptionsFairring::bounce_min_bytes)
+      .def_readwrite("pipe", &OptionsFairring::pipe)
+      .def_readwrite("pipe_min_bytes", &OptionsFairring::pipe_min_bytes)
+      .def_readwrite("pipe_blocks", &OptionsFairring::pipe_blocks)
+      .def_readwrite("pipe_channels", &OptionsFairring::pipe_channels)
+      .def_readwrite("pipe_slots", &OptionsFairring::pipe_slots)
+      .def_readwrite("pipe_chunk_bytes", &OptionsFairring::pipe_chunk_bytes)
+      .def_readwrite("pipe_stage_bytes", &OptionsFairring::pipe_stage_bytes)
+      .def_readwrite("pipe_stages", &OptionsFairring::pipe_stages)
+      .def_readwrite("direct_max_slices", &OptionsFairring::direct_max_slices)
+      .def_readwrite("direct_min_slice_bytes", &OptionsFairring::direct_min_slice_bytes)
       .def_readwrite("command_thread", &OptionsFairring::command_thread)
       .def_readwrite("blocking_wait", &OptionsFairring::blocking_wait)
       .def_readwrite("boot_id_override", &OptionsFairring::boot_id_override)
@@ -115,6 +127,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("deployment", &BackendFairring::deployment, py::call_guard<py::gil_scoped_release>())
       .def("trace", &BackendFairring::trace, py::call_guard<py::gil_scoped_release>())
       .def("check_health", &BackendFairring::checkHealth, py::call_guard<py::gil_scoped_release>())
+      .def("health", &BackendFairring::health, py::call_guard<py::gil_scoped_release>())
+      .def("release_symmetric", &BackendFairring::releaseSymmetric,
+           py::call_guard<py::gil_scoped_release>())
       .def("reset", &BackendFairring::reset, py::call_guard<py::gil_scoped_release>())
       .def("abort", &BackendFairring::abort, py::call_guard<py::gil_scoped_release>())
       .def("shutdown", &BackendFairring::shutdown, py::call_guard<py::gil_scoped_release>())
@@ -194,6 +209,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("scale") = 1.0, py::arg("wire_dtype") = py::none(), py::arg("algo") = "twoshot",
         py::arg("blocks") = 4, py::arg("half_bytes") = 1 << 20, py::arg("timeout_ms") = 2000,
         py::arg("silent_rank") = -1, py::arg("repeats") = 1);
+
+  m.def("emulated_pipe_allreduce", &emulatedPipeAllreduce, py::arg("inputs"), py::arg("op") = "sum",
+        py::arg("scale") = 1.0, py::arg("blocks") = 4, py::arg("chunk_bytes") = 64 << 10,
+        py::arg("slot_bytes") = 64 << 10, py::arg("slots") = 4, py::arg("stage_bytes") = 4096,
+        py::arg("stages") = 4, py::arg("timeout_ms") = 2000, py::arg("silent_rank") = -1,
+        py::arg("repeats") = 1);
 
   m.def("launch_count", []() { return (int64_t)(launchCount() + localLaunchCount()); });
   m.def("collective_launch_count", []() { return (int64_t)launchCount(); });

@@ -15,6 +15,7 @@
 #include "check.h"
 #include "engine.h"
 #include "kernels/kernels.h"
+#include "kernels/pipe_allreduce.h"
 
 namespace fairring {
 
@@ -197,6 +198,98 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
   std::memcpy(status.data_ptr(), status_host, sizeof(uint32_t) * W * kStatusWords);
   cudaFreeHost(status_host);
   return std::make_tuple(outs, status);
+}
+
+// The pipelined all-reduce (kernels/pipe_allreduce.h) with all ranks on one GPU,
+// peer-load flavour.  Every launch all-reduces the inputs in place; `repeats`
+// launches run back to back on one ring, so that chunk numbering and ring reuse
+// carry over from one launch to the next as they do in a real job.
+// Returns (inputs after the last launch, status words [world][kStatusWords]).
+std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedPipeAllreduce(
+    std::vector<at::Tensor> inputs, const std::string& op, double scale, int64_t blocks,
+    int64_t chunk_bytes, int64_t slot_bytes, int64_t slots, int64_t stage_bytes, int64_t stages,
+    int64_t timeout_ms, int64_t silent_rank, int64_t repeats) {
+  const int W = (int)inputs.size();
+  TORCH_CHECK(W >= 1 && W <= kMaxRanks, "1..", kMaxRanks, " emulated ranks");
+  TORCH_CHECK(blocks >= 1 && blocks <= kMaxBlocks, "blocks out of range");
+  TORCH_CHECK(chunk_bytes % kVecBytes == 0 && chunk_bytes > 0 && chunk_bytes <= slot_bytes,
+              "chunk must be whole vectors and fit a ring slot");
+  TORCH_CHECK(slots >= 2, "the ring needs at least two slots");
+  for (auto& t : inputs)
+    TORCH_CHECK(t.is_cuda() && t.device() == inputs[0].device() && t.is_contiguous() &&
+                    t.scalar_type() == inputs[0].scalar_type() && t.numel() == inputs[0].numel() &&
+                    (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15u) == 0,
+                "emulated ranks need same-shaped contiguous 16-byte aligned tensors on one GPU");
+  c10::cuda::CUDAGuard guard(inputs[0].device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  DType dt;
+  TORCH_CHECK(toDTypeEmu(inputs[0].scalar_type(), &dt), "unsupported dtype");
+  const RedOp rop = op == "max" ? RedOp::MAX : (op == "min" ? RedOp::MIN : RedOp::SUM);
+
+  auto u8 = inputs[0].options().dtype(at::kByte);
+  auto i32 = inputs[0].options().dtype(at::kInt);
+  std::vector<at::Tensor> rings, flags, seqs;
+  for (int r = 0; r < W; ++r) {
+    rings.push_back(at::zeros({slots * slot_bytes}, u8));
+    flags.push_back(at::zeros({(int64_t)(kPipeFlagBytes / sizeof(uint32_t))}, i32));
+    seqs.push_back(at::zeros({kMaxBlocks}, i32));
+  }
+  at::Tensor scratch = at::zeros({(int64_t)(kPipeFlagBytes / sizeof(uint32_t))}, i32);
+  uint32_t* status_host = nullptr;
+  FR_CUDA(cudaHostAlloc((void**)&status_host, sizeof(uint32_t) * (W * kStatusWords + 1),
+                        cudaHostAllocMapped));
+  std::memset(status_host, 0, sizeof(uint32_t) * (W * kStatusWords + 1));
+  uint32_t* status_dev = nullptr;
+  FR_CUDA(cudaHostGetDevicePointer((void**)&status_dev, status_host, 0));
+
+  std::vector<PipeChannelDev> chs(W);
+  for (int r = 0; r < W; ++r) {
+    PipeChannelDev& c = chs[r];
+    std::memset(&c, 0, sizeof(c));
+    for (int p = 0; p < W; ++p) {
+      c.ring[p] = static_cast<char*>(rings[p].data_ptr());
+      c.flags[p] = static_cast<uint32_t*>(flags[p].data_ptr());
+      // A silent rank's counters land in a pad nobody reads.
+      if (r == silent_rank && p != r) c.flags[p] = static_cast<uint32_t*>(scratch.data_ptr());
+    }
+    c.ring_mc = nullptr;
+    c.seq = static_cast<uint32_t*>(seqs[r].data_ptr());
+    c.status = status_dev + r * kStatusWords;
+    c.abort_flag = status_dev + W * kStatusWords;
+    c.slot_bytes = (uint64_t)slot_bytes;
+    c.timeout_ns = (uint64_t)timeout_ms * 1000000ull;
+    c.slots = (int32_t)slots;
+    c.world = W;
+    c.rank = r;
+  }
+  at::Tensor chs_dev = at::empty({(int64_t)(sizeof(PipeChannelDev) * W)}, u8);
+  FR_CUDA(cudaMemcpyAsync(chs_dev.data_ptr(), chs.data(), sizeof(PipeChannelDev) * W,
+                          cudaMemcpyHostToDevice, stream));
+  PipeArgs a;
+  std::memset(&a, 0, sizeof(a));
+  for (int r = 0; r < W; ++r) {
+    a.in[r] = inputs[r].data_ptr();
+    a.out[r] = inputs[r].data_ptr();
+  }
+  a.nbytes = inputs[0].numel() * inputs[0].element_size();
+  a.chunk_bytes = chunk_bytes;
+  a.scale = (float)scale;
+  a.op = (int32_t)rop;
+  a.dtype = (int32_t)dt;
+  a.nvls = 0;
+  a.stage_bytes = (int32_t)stage_bytes;
+  a.stages = (int32_t)stages;
+  for (int64_t rep = 0; rep < repeats; ++rep) {
+    cudaError_t e = launchPipeEmulated(static_cast<const PipeChannelDev*>(chs_dev.data_ptr()), a, W,
+                                       (int)blocks, stream);
+    TORCH_CHECK(e == cudaSuccess, "emulated launch of pipe_allreduce failed: ",
+                cudaGetErrorString(e));
+  }
+  FR_CUDA(cudaStreamSynchronize(stream));
+  at::Tensor status = at::zeros({W, kStatusWords}, at::kInt);
+  std::memcpy(status.data_ptr(), status_host, sizeof(uint32_t) * W * kStatusWords);
+  cudaFreeHost(status_host);
+  return std::make_tuple(inputs, status);
 }
 
 }  // namespace fairring

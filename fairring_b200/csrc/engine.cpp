@@ -21,17 +21,17 @@ const char* algoName(Algo a) {
     case Algo::HIER: return "hier";
     case Algo::NVLS: return "nvls";
     case Algo::NVLS_ONESHOT: return "nvls_oneshot";
-    case Algo::BOUNCE: return "bounce";
+    case Algo::PIPE: return "pipe";
   }
   return "?";
 }
 
 Algo parseAlgo(const std::string& s) {
   for (Algo a : {Algo::AUTO, Algo::ONESHOT, Algo::TWOSHOT, Algo::HIER, Algo::NVLS, Algo::NVLS_ONESHOT,
-                 Algo::BOUNCE})
+                 Algo::PIPE})
     if (s == algoName(a)) return a;
   FR_CHECK(false, "unknown FAIRRING_ALGO '", s,
-           "' (auto, oneshot, twoshot, hier, nvls, nvls_oneshot, bounce)");
+           "' (auto, oneshot, twoshot, hier, nvls, nvls_oneshot, pipe)");
   return Algo::AUTO;
 }
 
@@ -53,7 +53,6 @@ std::function<void()> CommandQueue::pop() {
 
 namespace {
 constexpr size_t kFlagPadBytes = (size_t)kMaxRanks * kMaxBlocks * sizeof(uint32_t);
-constexpr int kEventPool = 2048;
 constexpr size_t kTraceLen = 256;
 }  // namespace
 
@@ -69,21 +68,24 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
   // Kernels of different channels wait on their peers while resident.  If more
   // blocks were in flight than the GPU can hold at once, two GPUs could each
   // keep resident exactly the blocks whose partners are still queued on the
-  // other GPU, and nobody would move.  So: (channels x blocks) never exceeds
-  // the SM count.  The kernels are built for two resident blocks per SM
-  // (__launch_bounds__(512, 2)), which leaves the other half of every SM to
-  // the compute kernels the collectives overlap with, or to a second engine.
+  // other GPU, and nobody would move.  So: the blocks of all channels together
+  // never exceed the SM count.  Every kernel here occupies a whole SM per block
+  // (__launch_bounds__(512, 1), 128 registers per thread; the pipelined kernel
+  // also takes most of the shared memory).
   int sms = 0;
   FR_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_));
+  const bool want_pipe = cfg_.pipe != "off" && topo_.world > 1 && topo_.M == 1;
+  if (cfg_.pipe_blocks < 1) cfg_.pipe_blocks = 1;
+  if (cfg_.pipe_blocks > kMaxBlocks) cfg_.pipe_blocks = kMaxBlocks;
   // FAIRRING_SM_BUDGET further limits how many SMs the collectives may hold at
   // once, so that backward keeps most of the GPU while gradients are reduced.
-  const int budget = std::max(cfg_.blocks, std::min(sms, cfg_.sm_budget));
-  const int max_channels = std::max(1, budget / cfg_.blocks);
+  const int widest = want_pipe ? std::max(cfg_.blocks, cfg_.pipe_blocks) : cfg_.blocks;
+  const int budget = std::max(widest, std::min(sms, cfg_.sm_budget));
+  const int max_channels = std::max(1, budget / widest);
   if (cfg_.parallelism > max_channels) cfg_.parallelism = max_channels;
-  const bool want_bounce = cfg_.bounce != "off" && topo_.world > 1 && topo_.M == 1;
-  // With bounce buffers the budget is cut in three equal parts per channel:
-  // the two staging halves and the bounce buffer.
-  plan_ = planMemory(want_bounce ? cfg_.total_memory / 3 * 2 : cfg_.total_memory, cfg_.slice_bytes,
+  // With the pipelined kernel the budget is cut in three: two thirds for the
+  // staging slots of the channels, one third for its rings.
+  plan_ = planMemory(want_pipe ? cfg_.total_memory / 3 * 2 : cfg_.total_memory, cfg_.slice_bytes,
                      cfg_.parallelism, topo_.world, cfg_.min_half_bytes);
 
   alloc_.reset(new SymmAllocator(store_, topo_.rank, topo_.world, device_, cfg_.transport,
@@ -92,8 +94,23 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
   region_ = alloc_->allocate(flags_bytes_ + (size_t)plan_.slot_bytes * plan_.channels,
                              /*want_multicast=*/true);
 
-  if (want_bounce)
-    bounce_ = alloc_->allocate((size_t)plan_.half_bytes * plan_.channels, /*want_multicast=*/true);
+  if (want_pipe) {
+    pipe_channels_ = std::max(1, std::min<int>(cfg_.pipe_channels, plan_.channels));
+    if (cfg_.pipe_slots < 2) cfg_.pipe_slots = 2;
+    const int64_t ring_total = cfg_.total_memory / 3;
+    pipe_slot_bytes_ = roundDown(ring_total / pipe_channels_ / cfg_.pipe_slots, 4096);
+    if (pipe_slot_bytes_ > (8ll << 20)) pipe_slot_bytes_ = 8ll << 20;
+    if (pipe_slot_bytes_ < 4096) {
+      pipe_channels_ = 0;  // no room for rings: ordinary tensors take the staged kernels
+    } else {
+      pipe_flags_bytes_ = (size_t)roundUp((int64_t)(kPipeFlagBytes * pipe_channels_), 64 << 10);
+      pipe_region_ = alloc_->allocate(
+          pipe_flags_bytes_ + (size_t)pipe_slot_bytes_ * cfg_.pipe_slots * pipe_channels_,
+          /*want_multicast=*/true);
+      FR_CUDA(cudaMalloc(&pipe_seq_dev_, sizeof(uint32_t) * kMaxBlocks * pipe_channels_));
+      FR_CUDA(cudaMemset(pipe_seq_dev_, 0, sizeof(uint32_t) * kMaxBlocks * pipe_channels_));
+    }
+  }
 
   FR_CUDA(cudaMalloc(&seq_dev_, sizeof(uint32_t) * kMaxBlocks * plan_.channels));
   FR_CUDA(cudaMemset(seq_dev_, 0, sizeof(uint32_t) * kMaxBlocks * plan_.channels));
@@ -132,8 +149,33 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
   for (int c = 0; c < plan_.channels; ++c)
     FR_CUDA(cudaMemcpy(channels_dev_ + c, &channels_[c].dev, sizeof(ChannelDev),
                        cudaMemcpyHostToDevice));
-  events_.resize(kEventPool);
-  for (auto& e : events_) FR_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  if (pipe_channels_ > 0) {
+    std::vector<PipeChannelDev> pcs(pipe_channels_);
+    const size_t ring_bytes = (size_t)pipe_slot_bytes_ * cfg_.pipe_slots;
+    for (int c = 0; c < pipe_channels_; ++c) {
+      PipeChannelDev& pc = pcs[c];
+      std::memset(&pc, 0, sizeof(pc));
+      for (int r = 0; r < topo_.world; ++r) {
+        char* base = static_cast<char*>(pipe_region_.ptrs[r]);
+        pc.flags[r] = reinterpret_cast<uint32_t*>(base + kPipeFlagBytes * c);
+        pc.ring[r] = base + pipe_flags_bytes_ + ring_bytes * c;
+      }
+      pc.ring_mc = pipe_region_.mc_ptr
+                       ? static_cast<char*>(pipe_region_.mc_ptr) + pipe_flags_bytes_ + ring_bytes * c
+                       : nullptr;
+      pc.seq = pipe_seq_dev_ + (size_t)kMaxBlocks * c;
+      pc.status = channels_[c].dev.status;
+      pc.abort_flag = channels_[c].dev.abort_flag;
+      pc.slot_bytes = (uint64_t)pipe_slot_bytes_;
+      pc.timeout_ns = cfg_.device_timeout_ns;
+      pc.slots = cfg_.pipe_slots;
+      pc.world = topo_.world;
+      pc.rank = topo_.rank;
+    }
+    FR_CUDA(cudaMalloc(&pipe_channels_dev_, sizeof(PipeChannelDev) * pipe_channels_));
+    FR_CUDA(cudaMemcpy(pipe_channels_dev_, pcs.data(), sizeof(PipeChannelDev) * pipe_channels_,
+                       cudaMemcpyHostToDevice));
+  }
   FR_CUDA(cudaDeviceSynchronize());
   store_->barrier("engine/ready", topo_.world, cfg_.bootstrap_timeout);
 
@@ -157,8 +199,8 @@ Engine::~Engine() {
   cudaSetDevice(device_);
   cudaDeviceSynchronize();
   try {
-    for (auto& r : user_regions_) alloc_->release(r);
-    alloc_->release(bounce_);
+    for (auto& kv : user_regions_) alloc_->release(kv.second.reg);
+    alloc_->release(pipe_region_);
     alloc_->release(region_);
   } catch (const std::exception&) {
   }
@@ -171,24 +213,33 @@ Engine::~Engine() {
     // streams for the same reason, fairring/machine.cc:162-175.)
     if (ch.done) cudaEventDestroy(ch.done);
   }
-  for (auto& e : events_)
+  for (auto& e : free_events_)
     if (e) cudaEventDestroy(e);
+  if (pipe_seq_dev_) cudaFree(pipe_seq_dev_);
+  if (pipe_channels_dev_) cudaFree(pipe_channels_dev_);
   if (seq_dev_) cudaFree(seq_dev_);
   if (channels_dev_) cudaFree(channels_dev_);
   if (status_host_) cudaFreeHost(status_host_);
 }
 
-cudaEvent_t Engine::nextEvent() {
-  cudaEvent_t e = events_[next_event_];
-  next_event_ = (next_event_ + 1) % events_.size();
+cudaEvent_t Engine::begin(cudaStream_t caller) {
+  cudaEvent_t e = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(events_mu_);
+    if (!free_events_.empty()) {
+      e = free_events_.back();
+      free_events_.pop_back();
+    }
+  }
+  if (e == nullptr) FR_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  FR_CUDA(cudaEventRecord(e, caller));
   return e;
 }
 
-cudaEvent_t Engine::begin(cudaStream_t caller) {
-  std::lock_guard<std::mutex> lk(mu_);
-  cudaEvent_t e = nextEvent();
-  FR_CUDA(cudaEventRecord(e, caller));
-  return e;
+void Engine::releaseEvent(cudaEvent_t e) {
+  if (e == nullptr) return;
+  std::lock_guard<std::mutex> lk(events_mu_);
+  free_events_.push_back(e);
 }
 
 void Engine::submit(std::function<void()> fn) {
@@ -205,7 +256,11 @@ uint32_t Engine::health(std::string* what) const {
       if (what) {
         std::ostringstream os;
         os << "channel " << c << ": " << (s[0] == kStatusTimeout ? "timed out" : "aborted")
-           << " waiting for rank " << s[2] << " at barrier " << s[1] << " of collective " << s[3];
+           << " waiting for rank " << s[2];
+        if (s[1] >= 100)
+          os << " in the pipelined kernel (wait " << s[1] << ") at chunk " << s[3];
+        else
+          os << " at barrier " << s[1] << " of collective " << s[3];
         *what = os.str();
       }
       return s[0];
@@ -237,38 +292,103 @@ void Engine::reset() {
   store_->barrier(pfx + "/quiet", topo_.world, cfg_.bootstrap_timeout);
   FR_CUDA(cudaMemset(region_.ptrs[topo_.rank], 0, flags_bytes_));
   FR_CUDA(cudaMemset(seq_dev_, 0, sizeof(uint32_t) * kMaxBlocks * plan_.channels));
+  if (pipe_channels_ > 0) {
+    FR_CUDA(cudaMemset(pipe_region_.ptrs[topo_.rank], 0, pipe_flags_bytes_));
+    FR_CUDA(cudaMemset(pipe_seq_dev_, 0, sizeof(uint32_t) * kMaxBlocks * pipe_channels_));
+  }
   FR_CUDA(cudaDeviceSynchronize());
   std::memset(status_host_, 0, ((size_t)plan_.channels * kStatusWords + 16) * sizeof(uint32_t));
   poisoned_ = false;
   // Ranks may have issued different numbers of collectives before the failure:
   // start the round-robin over channels from the same place everywhere.
   next_channel_ = 0;
+  next_pipe_ = 0;
   store_->barrier(pfx + "/clean", topo_.world, cfg_.bootstrap_timeout);
 }
 
 void* Engine::allocSymmetric(size_t bytes) {
   std::lock_guard<std::mutex> lk(mu_);
   FR_CUDA(cudaSetDevice(device_));
-  user_regions_.push_back(alloc_->allocate(bytes, /*want_multicast=*/true));
-  return user_regions_.back().ptrs[topo_.rank];
+  releaseFreedLocked();  // every rank is here: a good moment to let go of dead regions
+  UserRegion u;
+  u.reg = alloc_->allocate(bytes, /*want_multicast=*/true);
+  u.id = next_region_id_++;
+  void* p = u.reg.ptrs[topo_.rank];
+  stats_.symmetric_regions += 1;
+  stats_.symmetric_bytes += u.reg.bytes;
+  user_regions_[reinterpret_cast<uintptr_t>(p)] = std::move(u);
+  return p;
+}
+
+void Engine::freeSymmetric(void* p) {
+  std::lock_guard<std::mutex> lk(mu_);
+  auto it = user_regions_.find(reinterpret_cast<uintptr_t>(p));
+  if (it == user_regions_.end() || it->second.freed) return;
+  it->second.freed = true;
+  stats_.symmetric_pending += 1;
+}
+
+// Unmapping is collective (peers hold mappings of this rank's memory, and the
+// allocator numbers its store keys), while a tensor dies whenever its last
+// reference goes.  So a dead region only waits here, and is released once every
+// rank reports it dead: each rank publishes the ids it has freed, all read all
+// lists, and the intersection is released in id order.
+int Engine::releaseFreedSymmetric() {
+  std::lock_guard<std::mutex> lk(mu_);
+  return releaseFreedLocked();
+}
+
+int Engine::releaseFreedLocked() {
+  if (topo_.world == 1 && stats_.symmetric_pending == 0) return 0;
+  FR_CUDA(cudaSetDevice(device_));
+  const std::string pfx = "engine/symfree" + std::to_string(release_round_++);
+  std::string mine = "L";  // never an empty value
+  for (auto& kv : user_regions_)
+    if (kv.second.freed) mine += std::to_string(kv.second.id) + ",";
+  store_->setString(pfx + "/" + std::to_string(topo_.rank), mine);
+  std::map<uint64_t, int> votes;
+  for (int r = 0; r < topo_.world; ++r) {
+    const std::string theirs = store_->getString(pfx + "/" + std::to_string(r));
+    size_t pos = 1;
+    while (pos < theirs.size()) {
+      const size_t comma = theirs.find(',', pos);
+      if (comma == std::string::npos) break;
+      ++votes[std::stoull(theirs.substr(pos, comma - pos))];
+      pos = comma + 1;
+    }
+  }
+  int released = 0;
+  for (auto& v : votes) {  // ascending id: the same order on every rank
+    if (v.second != topo_.world) continue;
+    for (auto it = user_regions_.begin(); it != user_regions_.end(); ++it) {
+      if (it->second.id != v.first) continue;
+      for (auto& ch : channels_) FR_CUDA(cudaStreamSynchronize(ch.stream));
+      stats_.symmetric_regions -= 1;
+      stats_.symmetric_bytes -= it->second.reg.bytes;
+      stats_.symmetric_pending -= 1;
+      alloc_->release(it->second.reg);
+      user_regions_.erase(it);
+      ++released;
+      break;
+    }
+  }
+  return released;
 }
 
 bool Engine::findSymmetric(const void* p, size_t bytes, const SymmRegion** reg, size_t* off) const {
-  const char* q = static_cast<const char*>(p);
-  for (const auto& r : user_regions_) {
-    const char* base = static_cast<const char*>(r.ptrs[topo_.rank]);
-    if (q >= base && q + bytes <= base + r.bytes) {
-      *reg = &r;
-      *off = (size_t)(q - base);
-      return true;
-    }
-  }
-  return false;
+  const uintptr_t q = reinterpret_cast<uintptr_t>(p);
+  auto it = user_regions_.upper_bound(q);
+  if (it == user_regions_.begin()) return false;
+  --it;
+  if (it->second.freed || q + bytes > it->first + it->second.reg.bytes) return false;
+  *reg = &it->second.reg;
+  *off = (size_t)(q - it->first);
+  return true;
 }
 
 // All-reduce in place on symmetric memory.  Returns false if the tensor does
 // not qualify (then the staged path is taken).
-bool Engine::runDirect(const CollectiveDesc& d, const std::function<Channel&()>& take) {
+bool Engine::runDirect(const CollectiveDesc& d, const std::function<Channel&(int)>& take) {
   if (cfg_.direct == "off" || d.kind != CollKind::ALLREDUCE || topo_.M != 1 || topo_.world < 2)
     return false;
   if (d.in != d.out || d.io != d.wire) return false;
@@ -308,60 +428,61 @@ bool Engine::runDirect(const CollectiveDesc& d, const std::function<Channel&()>&
     for (int r = 0; r < W; ++r) a.peer[r] = static_cast<char*>(reg->ptrs[r]) + o;
     a.mc = nvls ? static_cast<char*>(reg->mc_ptr) + o : nullptr;
     a.in[0] = a.out[0] = a.peer[topo_.rank];
-    launch(take(), nvls ? KernelId::NVLS_DIRECT : KernelId::P2P_DIRECT, a);
+    launch(take(-1), nvls ? KernelId::NVLS_DIRECT : KernelId::P2P_DIRECT, a);
     ++stats_.slices;
   }
   stats_.wire_bytes += bytes;
   return true;
 }
 
-// Ordinary tensor, big message: copy kernel in -> in-place kernel on the
-// symmetric bounce buffer -> copy kernel out, all on the channel's stream.  The
-// copy kernels do not wait on anybody, so they may be wide without touching
-// the residency bound.  The
-// kernel's closing barrier means every peer is done with this rank's buffer
-// before the copy-out (and the next copy-in) touches it, so one buffer per
-// channel is enough.
-bool Engine::runBounce(const CollectiveDesc& d, const std::function<Channel&()>& take) {
-  if (bounce_.ptrs.empty() || d.kind != CollKind::ALLREDUCE) return false;
-  if (d.io != d.wire || d.scale != 1.0f) return false;  // the fused kernels do scale and cast
-  const bool forced = cfg_.algo == Algo::BOUNCE;
+// Ordinary tensor: ONE launch of the pipelined kernel whatever the size.  The
+// message is not sliced: the kernel walks its chunks through the channel's
+// ring.  Consecutive messages alternate between the rings so that two launches
+// can overlap.
+bool Engine::runPipe(const CollectiveDesc& d, const std::function<Channel&(int)>& take) {
+  if (pipe_channels_ == 0 || d.kind != CollKind::ALLREDUCE || d.io != d.wire) return false;
+  const bool forced = cfg_.algo == Algo::PIPE;
   if (!forced && cfg_.algo != Algo::AUTO) return false;
   const int es = dtypeSize(d.io);
   const int64_t bytes = d.numel * es;
-  if (!forced && bytes < cfg_.bounce_min_bytes) return false;
-  if (bytes <= cfg_.oneshot_max_bytes) return false;
-  bool nvls = bounce_.mc_ptr != nullptr && nvlsSupported(d.wire, d.op) && cfg_.direct != "p2p";
-  if (cfg_.direct == "auto" && topo_.world <= 2) nvls = false;
+  if (bytes <= 0) return false;
+  if (!forced && bytes < cfg_.pipe_min_bytes) return false;
+  if (((reinterpret_cast<uintptr_t>(d.in) | reinterpret_cast<uintptr_t>(d.out)) & 15u) != 0)
+    return false;  // bulk copies need 16-byte aligned addresses
   const int W = topo_.world;
-  const int64_t V = kVecBytes / es;
-  int64_t cap = std::max<int64_t>(cfg_.direct_min_slice_bytes,
-                                  ceilDiv(bytes, (int64_t)channels_.size()));
-  if (cap > plan_.half_bytes) cap = plan_.half_bytes;
-  int64_t slice_elems = roundDown(cap / es, V * W);
-  if (slice_elems < V * W) slice_elems = V * W;
-  const char* in = static_cast<const char*>(d.in);
-  char* out = static_cast<char*>(d.out);
-  for (int64_t start = 0; start < d.numel; start += slice_elems) {
-    const int64_t n = std::min(slice_elems, d.numel - start);
-    Channel& ch = take();
-    const size_t o = (size_t)(&ch - channels_.data()) * (size_t)plan_.half_bytes;
-    char* mine = static_cast<char*>(bounce_.ptrs[topo_.rank]) + o;
-    FR_CUDA(launchCopy(mine, in + start * es, (size_t)n * es, cfg_.bounce_copy_blocks, ch.stream));
-    OpArgs a{};
-    a.seg = allreduceSeg(n, es, W);
-    a.scale = 1.0f;
-    a.op = (int32_t)d.op;
-    a.io_dtype = a.wire_dtype = (int32_t)d.io;
-    a.flags = kAdvanceSeq;
-    for (int r = 0; r < W; ++r) a.peer[r] = static_cast<char*>(bounce_.ptrs[r]) + o;
-    a.mc = nvls ? static_cast<char*>(bounce_.mc_ptr) + o : nullptr;
-    a.in[0] = a.out[0] = mine;
-    launch(ch, nvls ? KernelId::NVLS_DIRECT : KernelId::P2P_DIRECT, a);
-    FR_CUDA(launchCopy(out + start * es, mine, (size_t)n * es, cfg_.bounce_copy_blocks, ch.stream));
-    ++stats_.slices;
-    ++stats_.bounce_slices;
+  bool nvls = pipe_region_.mc_ptr != nullptr && nvlsSupported(d.wire, d.op) && cfg_.direct != "p2p";
+  if (cfg_.direct == "auto" && W <= 2) nvls = false;
+  // Small messages: fewer blocks, so that a block's piece of a sub-chunk stays
+  // worth a bulk copy (8 KiB or more).
+  int blocks = (int)std::min<int64_t>(cfg_.pipe_blocks, std::max<int64_t>(1, bytes / ((int64_t)W * 8192)));
+  // Chunk: the whole message when it is small; otherwise an eighth of it,
+  // between 512 KiB and a ring slot.
+  const int64_t quantum = (int64_t)kVecBytes * W * blocks;
+  int64_t chunk = cfg_.pipe_chunk_bytes;
+  if (chunk <= 0) {
+    chunk = bytes <= (1 << 20) ? bytes : std::max<int64_t>(512 << 10, bytes / 8);
   }
+  chunk = roundUp(chunk, quantum);
+  if (chunk > pipe_slot_bytes_) chunk = roundDown(pipe_slot_bytes_, kVecBytes);
+  const int pc = (int)(next_pipe_++ % (uint64_t)pipe_channels_);
+  Channel& ch = take(pc);
+  PipeArgs a{};
+  a.in[0] = d.in;
+  a.out[0] = d.out;
+  a.nbytes = bytes;
+  a.chunk_bytes = chunk;
+  a.scale = d.scale;
+  a.op = (int32_t)d.op;
+  a.dtype = (int32_t)d.io;
+  a.nvls = nvls ? 1 : 0;
+  a.stage_bytes = cfg_.pipe_stage_bytes;
+  a.stages = cfg_.pipe_stages;
+  cudaError_t e = launchPipeAllreduce(pipe_channels_dev_ + pc, a, blocks, ch.stream);
+  FR_CHECK(e == cudaSuccess, "launch of pipe_allreduce failed: ", cudaGetErrorString(e));
+  ++stats_.launches[(size_t)KernelId::PIPE];
+  if (cur_.launches == 0) cur_.first_kernel = (int32_t)KernelId::PIPE;
+  ++cur_.launches;
+  ++stats_.slices;
   stats_.wire_bytes += (uint64_t)bytes;
   return true;
 }
@@ -389,7 +510,12 @@ std::string Engine::describe() const {
      << " transport=" << alloc_->describe() << " nvls=" << (nvlsAvailable() ? "yes" : "no")
      << " channels=" << plan_.channels << " half_slot=" << plan_.half_bytes
      << "B max_slice=" << plan_.max_slice_bytes << "B blocks=" << cfg_.blocks
-     << " algo=" << algoName(cfg_.algo) << " bounce=" << (bounce_.ptrs.empty() ? "no" : "yes");
+     << " algo=" << algoName(cfg_.algo) << " pipe=";
+  if (pipe_channels_ > 0)
+    os << pipe_channels_ << "x" << cfg_.pipe_slots << "x" << pipe_slot_bytes_ << "B/" << cfg_.pipe_blocks
+       << "blocks";
+  else
+    os << "no";
   return os.str();
 }
 
@@ -401,7 +527,7 @@ Algo Engine::chooseAllreduce(int64_t wire_bytes, DType wire, RedOp op) const {
   Algo a = cfg_.algo;
   if (a == Algo::ONESHOT && !oneshot_fits) a = Algo::AUTO;
   if ((a == Algo::NVLS || a == Algo::NVLS_ONESHOT) && !nvls_ok) a = Algo::AUTO;
-  if (a == Algo::BOUNCE) a = Algo::AUTO;  // this message did not qualify for the bounce path
+  if (a == Algo::PIPE) a = Algo::AUTO;  // this message did not qualify for the pipelined kernel
   if (a == Algo::TWOSHOT && topo_.M > 1) a = Algo::HIER;
   if (a != Algo::AUTO) return a;
   if (wire_bytes <= cfg_.oneshot_max_bytes && oneshot_fits) return Algo::ONESHOT;
@@ -469,8 +595,9 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after,
   const int ies = dtypeSize(d.io), wes = dtypeSize(d.wire);
   const int64_t V = kVecBytes / wes;
   std::vector<int> used;
-  std::function<Channel&()> take = [&]() -> Channel& {
-    const int c = (int)(next_channel_++ % channels_.size());
+  // take(-1): the next channel in turn; take(c): channel c.
+  std::function<Channel&(int)> take = [&](int want) -> Channel& {
+    const int c = want >= 0 ? want : (int)(next_channel_++ % channels_.size());
     if (std::find(used.begin(), used.end(), c) == used.end()) {
       FR_CUDA(cudaStreamWaitEvent(channels_[c].stream, after, 0));
       used.push_back(c);
@@ -507,14 +634,14 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after,
     }
   } finish{this, &used, t_begin, slices_before};
 
-  if (runDirect(d, take) || runBounce(d, take)) {
+  if (runDirect(d, take) || runPipe(d, take)) {
     // nothing else to do
   } else if (d.kind == CollKind::ALLREDUCE) {
     const int64_t bytes = d.numel * wes;
     const Algo whole = chooseAllreduce(bytes, d.wire, d.op);
     if (whole == Algo::ONESHOT ||
         (whole == Algo::NVLS_ONESHOT && bytes <= plan_.max_slice_bytes)) {
-      runAllreduceSlice(take(), d, in, out, d.numel, whole);
+      runAllreduceSlice(take(-1), d, in, out, d.numel, whole);
       ++stats_.slices;
     } else {
       // A big message is spread over all channels (more blocks in flight),
@@ -533,7 +660,7 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after,
         if (a == Algo::ONESHOT || a == Algo::NVLS_ONESHOT) a = chooseAllreduce(n * wes, d.wire, d.op);
         if (sp.num_slices > 1 && a == Algo::ONESHOT) a = topo_.M > 1 ? Algo::HIER : Algo::TWOSHOT;
         if (sp.num_slices > 1 && a == Algo::NVLS_ONESHOT) a = Algo::NVLS;
-        runAllreduceSlice(take(), d, in + off * ies, out + off * ies, n, a);
+        runAllreduceSlice(take(-1), d, in + off * ies, out + off * ies, n, a);
         ++stats_.slices;
       }
     }
@@ -551,7 +678,7 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after,
       a.op = (int32_t)d.op;
       a.io_dtype = (int32_t)d.io;
       a.wire_dtype = (int32_t)d.wire;
-      Channel& ch = take();
+      Channel& ch = take(-1);
       if (d.kind == CollKind::REDUCE_SCATTER) {
         if (topo_.M == 1) {
           a.flags = kToUser | kAdvanceSeq;
@@ -574,7 +701,7 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after,
   }
 
   if (used.empty()) {  // zero elements: still give the caller a stream ordered after `after`
-    Channel& ch = take();
+    Channel& ch = take(-1);
     return ch.stream;
   }
   if (used_streams)

@@ -16,6 +16,7 @@
 #include <condition_variable>
 #include <deque>
 #include <functional>
+#include <map>
 #include <memory>
 #include <mutex>
 #include <string>
@@ -23,13 +24,14 @@
 #include <vector>
 
 #include "kernels/kernels.h"
+#include "kernels/pipe_allreduce.h"
 #include "kvstore.h"
 #include "layout.h"
 #include "symmem.h"
 
 namespace fairring {
 
-enum class Algo : int32_t { AUTO = 0, ONESHOT, TWOSHOT, HIER, NVLS, NVLS_ONESHOT, BOUNCE };
+enum class Algo : int32_t { AUTO = 0, ONESHOT, TWOSHOT, HIER, NVLS, NVLS_ONESHOT, PIPE };
 const char* algoName(Algo a);
 Algo parseAlgo(const std::string& s);
 
@@ -54,13 +56,18 @@ struct EngineConfig {
   std::string direct = "auto";
   int64_t direct_min_slice_bytes = 2ll << 20;  // a message is split over channels down to this
   int32_t direct_max_slices = 2;               // ... but an in-place message into at most this many
-  // Ordinary (non-symmetric) tensors of at least bounce_min_bytes are copied by
-  // a wide kernel into a symmetric bounce buffer, reduced there in place by the
-  // zero-copy kernel and copied back.  "auto" | "on" | "off".  A third of the
-  // memory budget becomes bounce buffers when this is enabled.
-  std::string bounce = "auto";
-  int32_t bounce_copy_blocks = 96;
-  int64_t bounce_min_bytes = 32ll << 20;
+  // Ordinary (non-symmetric) tensors of at least pipe_min_bytes take the
+  // pipelined kernel (kernels/pipe_allreduce.h): one launch whatever the size.
+  // "auto" | "on" | "off".  A third of the memory budget becomes its staging
+  // rings when it is enabled.
+  std::string pipe = "auto";
+  int64_t pipe_min_bytes = 512 << 10;
+  int32_t pipe_blocks = 16;        // thread blocks of one pipelined launch (fewer for small messages)
+  int32_t pipe_channels = 2;       // rings, i.e. pipelined launches that may overlap
+  int32_t pipe_slots = 4;          // ring length in chunks
+  int64_t pipe_chunk_bytes = 0;    // 0: chosen from the message size
+  int32_t pipe_stage_bytes = 16 << 10;  // one shared-memory stage of a copy role
+  int32_t pipe_stages = 6;
   std::chrono::milliseconds bootstrap_timeout{120000};
 };
 
@@ -81,7 +88,9 @@ struct EngineStats {
   uint64_t collectives = 0;
   uint64_t slices = 0;
   uint64_t wire_bytes = 0;
-  uint64_t bounce_slices = 0;
+  uint64_t symmetric_regions = 0;   // live allocations handed out by allocSymmetric
+  uint64_t symmetric_bytes = 0;     // ... and their size (outside the staging budget)
+  uint64_t symmetric_pending = 0;   // freed by their tensor, not yet released by all ranks
   std::array<uint64_t, (size_t)KernelId::kCount> launches{};
 };
 
@@ -117,8 +126,11 @@ class Engine {
   ~Engine();
 
   // Record "the caller's work so far" so that a later run() can order itself
-  // after it; cheap, called on the caller's thread.
+  // after it; cheap, called on the caller's thread.  The event belongs to the
+  // caller until it hands it back with releaseEvent(): it is never re-recorded
+  // behind a holder's back.
   cudaEvent_t begin(cudaStream_t caller);
+  void releaseEvent(cudaEvent_t e);
   // Enqueue the whole collective.  Returns the side stream on which everything
   // it launched is ordered; the caller records its completion event there.
   // `used` (optional) receives every side stream the collective touched.
@@ -137,9 +149,15 @@ class Engine {
   void reset();
 
   // Collective: symmetric device memory (peer-mapped everywhere, multicast
-  // alias when available) that lives as long as the engine.  all_reduce on a
-  // tensor inside it runs in place with no staging copies.
+  // alias when available).  all_reduce on a tensor inside it runs in place with
+  // no staging copies.  It is not part of the staging budget.
   void* allocSymmetric(size_t bytes);
+  // Not collective, any thread: the holder of `p` (from allocSymmetric) is done
+  // with it.  The memory is unmapped at the next allocSymmetric() or
+  // releaseFreedSymmetric() on which every rank has let go of the same region.
+  void freeSymmetric(void* p);
+  // Collective: release the regions every rank has freed; returns how many.
+  int releaseFreedSymmetric();
 
   const Topo& topo() const { return topo_; }
   const MemoryPlan& plan() const { return plan_; }
@@ -161,10 +179,10 @@ class Engine {
   void launch(Channel& ch, KernelId id, const OpArgs& a);
   void runAllreduceSlice(Channel& ch, const CollectiveDesc& d, const void* in, void* out,
                          int64_t n, Algo algo);
-  cudaEvent_t nextEvent();
   bool findSymmetric(const void* p, size_t bytes, const SymmRegion** reg, size_t* off) const;
-  bool runDirect(const CollectiveDesc& d, const std::function<Channel&()>& take);
-  bool runBounce(const CollectiveDesc& d, const std::function<Channel&()>& take);
+  int releaseFreedLocked();
+  bool runDirect(const CollectiveDesc& d, const std::function<Channel&(int)>& take);
+  bool runPipe(const CollectiveDesc& d, const std::function<Channel&(int)>& take);
 
   std::shared_ptr<KvStore> store_;
   Topo topo_;
@@ -173,16 +191,30 @@ class Engine {
   MemoryPlan plan_;
   std::unique_ptr<SymmAllocator> alloc_;
   SymmRegion region_;
-  std::vector<SymmRegion> user_regions_;
-  SymmRegion bounce_;  // [channels][half_bytes], empty when disabled
+  struct UserRegion {
+    SymmRegion reg;
+    uint64_t id = 0;    // allocation number: the same on every rank
+    bool freed = false;
+  };
+  std::map<uintptr_t, UserRegion> user_regions_;  // by local base address
+  uint64_t next_region_id_ = 0;
+  int release_round_ = 0;
+  // Pipelined kernel: flag pads of all its channels, then one ring per channel.
+  SymmRegion pipe_region_;
+  size_t pipe_flags_bytes_ = 0;
+  int64_t pipe_slot_bytes_ = 0;
+  int pipe_channels_ = 0;
+  uint64_t next_pipe_ = 0;
+  uint32_t* pipe_seq_dev_ = nullptr;
+  PipeChannelDev* pipe_channels_dev_ = nullptr;
   size_t flags_bytes_ = 0;
   uint32_t* seq_dev_ = nullptr;
   uint32_t* status_host_ = nullptr;  // pinned + mapped: [channels][kStatusWords], then abort word
   uint32_t* status_dev_ = nullptr;
   std::vector<Channel> channels_;
   ChannelDev* channels_dev_ = nullptr;  // device copy of channels_[i].dev
-  std::vector<cudaEvent_t> events_;
-  size_t next_event_ = 0;
+  std::vector<cudaEvent_t> free_events_;  // created on demand, reused after releaseEvent()
+  std::mutex events_mu_;
   uint64_t next_channel_ = 0;
   std::mutex mu_;
   EngineStats stats_;

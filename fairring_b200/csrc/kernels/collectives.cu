@@ -53,6 +53,7 @@ const char* kernelName(KernelId id) {
     case KernelId::NVLS_ONESHOT: return "nvls_oneshot_allreduce";
     case KernelId::P2P_DIRECT: return "direct_allreduce";
     case KernelId::NVLS_DIRECT: return "nvls_direct_allreduce";
+    case KernelId::PIPE: return "pipe_allreduce";
     default: return "?";
   }
 }
@@ -108,5 +109,6 @@ cudaError_t launchEmulated(KernelId id, const ChannelDev* chs_dev, const OpArgs&
 }
 
 uint64_t launchCount() { return g_launches.load(std::memory_order_relaxed); }
+void countLaunch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 }  // namespace fairring

@@ -68,6 +68,8 @@ enum class KernelId : int32_t {
   NVLS_ONESHOT,         // multimem.ld_reduce the whole message
   P2P_DIRECT,           // in place on symmetric memory: pull + reduce own chunk, push it to all
   NVLS_DIRECT,          // in place on symmetric memory: multimem.ld_reduce + multimem.st
+  PIPE,                 // ordinary tensors: copy-in / reduce / copy-out pipelined over chunks
+                        // (pipe_allreduce.h; counted here, launched through launchPipeAllreduce)
   kCount
 };
 
@@ -95,5 +97,7 @@ cudaError_t launchEmulated(KernelId id, const ChannelDev* chs_dev, const OpArgs&
 
 // Number of kernels this library has launched in this process.
 uint64_t launchCount();
+// Adds one to that number (for kernels launched outside launchCollective).
+void countLaunch();
 
 }  // namespace fairring

@@ -88,6 +88,12 @@ class FlatDataParallel(nn.Module):
                 raise ValueError("FlatDataParallel expects fp32 parameters on one device")
         self.device = dev
         self.backend = get_backend(self.process_group, "cuda")
+        # On any other c10d backend (NCCL, say) the buckets are averaged with a
+        # plain asynchronous all_reduce: same buffers, same bucket order, same
+        # optimizer, only the transport differs.
+        self._fused = hasattr(self.backend, "allreduce_fused")
+        if not self._fused and wire_dtype is not None:
+            raise ValueError("a wire dtype needs the fairring backend (fused cast)")
 
         # Backward produces gradients roughly in reverse registration order, so
         # lay the buffers out in that order: bucket 0 fills first.
@@ -102,7 +108,7 @@ class FlatDataParallel(nn.Module):
         # rank's buffer is peer-mapped (and multicast-mapped) everywhere, so a
         # bucket is all-reduced in place by the switch, with no staging copies.
         self.symmetric = False
-        if symmetric_grads and self.world > 1 and wire_dtype is None:
+        if symmetric_grads and self.world > 1 and wire_dtype is None and self._fused:
             try:
                 with torch.cuda.device(dev):
                     self.flat_grad = self.backend.symmetric_empty(total, torch.float32)
@@ -114,6 +120,12 @@ class FlatDataParallel(nn.Module):
             self.flat_grad = torch.zeros(total, device=dev, dtype=torch.float32)
         self._params = order
         self._offsets = offsets
+        # name -> (offset, numel, shape) of the fp32 master copy, for state_dict()
+        ids = {id(p): i for i, p in enumerate(order)}
+        self._named = {n: (offsets[ids[id(p)]], p.numel(), tuple(p.shape))
+                       for n, p in module.named_parameters() if id(p) in ids}
+        self._index_of = dict(ids)
+        self._seen = [False] * len(order)
         for p, off in zip(order, offsets):
             view = self.flat_param[off:off + p.numel()].view_as(p)
             view.copy_(p.data)
@@ -167,6 +179,7 @@ class FlatDataParallel(nn.Module):
                     mod._parameters[name] = shadow
                     self._off_of[id(shadow)] = off
                     self._bucket_of[id(shadow)] = self._bucket_of[id(master)]
+                    self._index_of[id(shadow)] = self._index_of[id(master)]
                     shadow.register_post_accumulate_grad_hook(self._on_grad)
 
     # -- public ------------------------------------------------------------
@@ -178,8 +191,39 @@ class FlatDataParallel(nn.Module):
         return self.module(*args, **kwargs)
 
     def zero_grad(self, set_to_none: bool = True) -> None:  # noqa: ARG002
-        """Nothing to clear: every backward overwrites the flat gradient buffer."""
+        """Nothing to clear here: every backward overwrites the ranges of the
+        parameters that received a gradient and zeroes the ranges of those that
+        did not (see ``_finish_backward``)."""
         self._accumulate = False
+
+    def state_dict(self, *args, **kwargs) -> dict:
+        """The wrapped module's state with the fp32 master weights (with
+        ``bf16_shadow`` the module itself only holds bf16 copies of the
+        ``nn.Linear`` parameters)."""
+        sd = self.module.state_dict(*args, **kwargs)
+        prefix = kwargs.get("prefix", "")
+        for name, (off, n, shape) in self._named.items():
+            sd[prefix + name] = self.flat_param[off:off + n].view(shape).detach().clone()
+        return sd
+
+    def load_state_dict(self, state_dict: dict, strict: bool = True):
+        """Load into the fp32 master buffer (and refresh the bf16 shadow)."""
+        missing = [n for n in self._named if n not in state_dict]
+        if strict and missing:
+            raise KeyError(f"missing parameters in state_dict: {missing[:5]}")
+        with torch.no_grad():
+            for name, (off, n, shape) in self._named.items():
+                if name in state_dict:
+                    self.flat_param[off:off + n].view(shape).copy_(state_dict[name])
+            if self.flat_shadow is not None:
+                self.flat_shadow.copy_(self.flat_param)
+        rest = {k: v for k, v in state_dict.items() if k not in self._named}
+        buffers = dict(self.module.named_buffers())
+        for k, v in rest.items():
+            if k in buffers:
+                buffers[k].copy_(v)
+            elif strict:
+                raise KeyError(f"unexpected key in state_dict: {k}")
 
     def no_sync(self):
         """Context manager: accumulate locally, skip the all-reduce (like DDP's)."""
@@ -207,6 +251,7 @@ class FlatDataParallel(nn.Module):
         else:
             dst.copy_(g)
         p.grad = None  # the flat buffer is the gradient; views are handed out by grads()
+        self._seen[self._index_of[id(p)]] = True
         if not self._callback_queued:
             torch.autograd.Variable._execution_engine.queue_callback(self._finish_backward)
             self._callback_queued = True
@@ -223,11 +268,25 @@ class FlatDataParallel(nn.Module):
         if self.world == 1:
             return
         s, e = self._buckets[b]
-        self._works.append(
-            self.backend.allreduce_fused(self.flat_grad[s:e], 1.0 / self.world, self.wire_dtype, "sum")
-        )
+        if self._fused:
+            self._works.append(
+                self.backend.allreduce_fused(self.flat_grad[s:e], 1.0 / self.world, self.wire_dtype, "sum")
+            )
+        else:
+            self._works.append(
+                dist.all_reduce(self.flat_grad[s:e], op=dist.ReduceOp.AVG, group=self.process_group,
+                                async_op=True)
+            )
 
     def _finish_backward(self) -> None:
+        # A parameter that received no gradient in this backward must not keep
+        # the (already averaged) gradient of an earlier step.
+        if not self._accumulate and not all(self._seen):
+            for i, seen in enumerate(self._seen):
+                if not seen:
+                    off = self._offsets[i]
+                    self.flat_grad[off:off + self._params[i].numel()].zero_()
+        self._seen = [False] * len(self._params)
         if self.require_backward_grad_sync:
             while self._next_to_launch < len(self._buckets):  # parameters that got no gradient
                 self._launch(self._next_to_launch)
@@ -235,6 +294,14 @@ class FlatDataParallel(nn.Module):
             for w in self._works:
                 w.wait()  # stream-level: the compute stream waits, the host does not
             self._accumulate = False
+            # Host-side look at the kernels' status words (no synchronisation): a
+            # device-side wait that gave up in an earlier step surfaces here, before
+            # the optimizer consumes another set of gradients.
+            if self._fused and self.world > 1:
+                err = self.backend.health()
+                if err:
+                    raise RuntimeError(f"fairring: a gradient all-reduce failed ({err}); "
+                                       "call backend.reset() on every rank to recover")
         else:
             self._accumulate = True
         self._works = []

@@ -67,7 +67,7 @@ def _suite(rank, world, check_ddp):
     for i, b in enumerate(bufs):
         assert float(b[0]) == sum(r + i for r in range(world)) and float(b[-1]) == float(b[0])
 
-    # a big ordinary tensor (copy-engine bounce path when enabled), odd length
+    # a big ordinary tensor (the pipelined kernel when enabled), odd length
     x = seeded(12_000_001, torch.float32, rank, 9).to(dev)
     dist.all_reduce(x)
     expect = torch.stack([seeded(12_000_001, torch.float32, r, 9).double() for r in range(world)]).sum(0)
@@ -178,8 +178,9 @@ CONFIGS = {
     "twoshot_no_nvls": {"FAIRRING_NVLS": "off", "FAIRRING_ALGO": "twoshot"},
     "nvls": {"FAIRRING_ALGO": "nvls"},
     "nvls_oneshot": {"FAIRRING_ALGO": "nvls_oneshot"},
-    "bounce": {"FAIRRING_ALGO": "bounce", "FAIRRING_BOUNCE": "on"},
-    "bounce_p2p": {"FAIRRING_ALGO": "bounce", "FAIRRING_BOUNCE": "on", "FAIRRING_NVLS": "off"},
+    "pipe": {"FAIRRING_ALGO": "pipe", "FAIRRING_DIRECT": "nvls"},
+    "pipe_p2p": {"FAIRRING_ALGO": "pipe", "FAIRRING_NVLS": "off"},
+    "pipe_off": {"FAIRRING_PIPE": "off"},
     "hier_three_kernels": {"FAIRRING_ALGO": "hier", "FAIRRING_NVLS": "off"},
     "ipc_transport_cmd_thread": {"FAIRRING_TRANSPORT": "ipc", "FAIRRING_COMMAND_THREAD": "1"},
     "machines_of_one_gpu": {"FAIRRING_GPUS_PER_MACHINE": "1", "FAIRRING_NVLS": "off"},
@@ -204,8 +205,12 @@ def test_backend_on_gpus(name):
         assert stats["nvls"] == 0 and stats["launch_twoshot_allreduce"] > 0
     if name in ("nvls", "nvls_oneshot") and stats["nvls"] == 1:
         assert stats["launch_nvls_allreduce"] + stats["launch_nvls_oneshot_allreduce"] > 0
-    if name.startswith("bounce"):
-        assert stats["gpu_bounce_slices"] > 0
+    if name.startswith("pipe") and name != "pipe_off":
+        assert stats["launch_pipe_allreduce"] > 0
+    if name == "pipe_off":
+        assert stats["launch_pipe_allreduce"] == 0
+    if name == "auto":
+        assert stats["launch_pipe_allreduce"] > 0
     if name == "hier_three_kernels":
         assert stats["launch_rs_intragroup"] > 0 and stats["launch_ag_intragroup"] > 0
     if name == "machines_of_two_gpus" and world >= 4:
