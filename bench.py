@@ -227,9 +227,12 @@ def main():
             # adjacent views of one storage, fairring/utils.h:363-386); so the
             # start-up sync is done here with broadcast, which the reference
             # delegates to NCCL.
+            # (async_op=True: for a blocking call torch's NCCL backend makes no
+            # Future, and the reference wraps exactly that Future,
+            # fairring/process_group.cc:124-129.)
             if world > 1:
                 for p in model.parameters():
-                    dist.broadcast(p.data, src=0)
+                    dist.broadcast(p.data, src=0, async_op=True).wait()
             ddp = DDP(model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb,
                       gradient_as_bucket_view=True, init_sync=False)
         else:
@@ -369,6 +372,13 @@ def main():
             out["check"] = check
         print(json.dumps(out), flush=True)
     sync_all()
+    if reference:
+        # The reference leaves streams and recorded tensors behind that outlive the
+        # CUDA context at interpreter shutdown (it leaks its streams on purpose,
+        # fairring/machine.cc:162-175): leave without running finalizers.
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     dist.destroy_process_group()
     return 0
 

@@ -22,13 +22,18 @@ FAIRRING_PARALLELISM           slices in flight = side streams/channels (default
 FAIRRING_SLICE_SIZE            max bytes per slice (default 25 MiB, DDP's bucket size)
 FAIRRING_GPUS_PER_MACHINE      D of the M x D grouping (default: all ranks of a host)
 FAIRRING_RANK_LAYOUT           "standard" (rank = m*D+d) or "favorable" (rank = d*M+m)
-FAIRRING_ALGO                  auto | oneshot | twoshot | hier | nvls | nvls_oneshot | pipe
+FAIRRING_ALGO                  auto | ll | oneshot | twoshot | hier | nvls | nvls_oneshot | pipe
 FAIRRING_BLOCKS                thread blocks per kernel (default 16, max 64)
 FAIRRING_SM_BUDGET             SMs the collectives may occupy at once (default 64): the number
                                of channels is at most SM_BUDGET / BLOCKS.  Raise it (up to the
                                SM count) for stand-alone all-reduce bandwidth, keep it low to
                                leave the GPU to backward
+FAIRRING_LL_MAX                largest message (bytes) for the flag-in-data kernel (default 32 KiB;
+                               0 turns it off); FAIRRING_LL_CHANNELS channels carry its areas
+FAIRRING_INLINE_SMALL          1 (default): a blocking all_reduce that fits that kernel runs on the
+                               caller's own stream
 FAIRRING_ONESHOT_MAX           largest message (bytes) for the one-shot kernel
+FAIRRING_DIRECT_UNROLL         16-byte multimem loads a thread keeps in flight in the in-place kernel
 FAIRRING_NVLS                  auto | on | off   (NVSwitch multicast kernels)
 FAIRRING_NVLS_MIN              smallest message (bytes) for the NVLS two-shot kernel
 FAIRRING_NVLS_ONESHOT_MAX      largest message (bytes) for the NVLS one-shot kernel
@@ -50,6 +55,8 @@ FAIRRING_DIRECT_MIN_SLICE      ... down to slices of this many bytes
 FAIRRING_DEVICE_TIMEOUT_MS     limit of one device-side wait on a peer (default: the process
                                group's timeout; a wait that runs out leaves the tensor
                                unreduced and poisons the engine until reset())
+FAIRRING_TUNING_TABLE          path of the measured thresholds (default: tuning.json beside this
+                               file, keyed by world size); "off" ignores it
 FAIRRING_COMMAND_THREAD        1: enqueue kernels from a dedicated thread
 FAIRRING_BLOCKING_WAIT         1: Work.wait() blocks the host and reports kernel failures
 =============================  ==========================================================
@@ -101,9 +108,44 @@ def _env_int(name: str, default: int) -> int:
         return default
 
 
-def options_from_env(timeout: timedelta | None = None) -> "_C.Options":
-    """Build backend options from the FAIRRING_* environment variables."""
+# Option name -> the environment variable that overrides it.
+_TUNABLES = {
+    "ll_max_bytes": "FAIRRING_LL_MAX",
+    "oneshot_max_bytes": "FAIRRING_ONESHOT_MAX",
+    "nvls_oneshot_max_bytes": "FAIRRING_NVLS_ONESHOT_MAX",
+    "pipe_min_bytes": "FAIRRING_PIPE_MIN",
+    "pipe_blocks": "FAIRRING_PIPE_BLOCKS",
+    "blocks": "FAIRRING_BLOCKS",
+    "direct_max_slices": "FAIRRING_DIRECT_MAX_SLICES",
+    "direct_unroll": "FAIRRING_DIRECT_UNROLL",
+}
+
+
+def tuning_table(world: int) -> dict:
+    """Measured thresholds for this world size from ``tuning.json`` next to this
+    file (written by ``python -m fairring_b200.bench.tune --write-table``), or
+    an empty dict.  ``FAIRRING_TUNING_TABLE=off`` ignores the file; a path
+    names another file."""
+    where = os.environ.get("FAIRRING_TUNING_TABLE", "")
+    if where.lower() == "off":
+        return {}
+    path = Path(where) if where else _HERE / "tuning.json"
+    try:
+        import json
+
+        table = json.loads(path.read_text()).get(str(world), {})
+    except (OSError, ValueError):
+        return {}
+    return {k: int(v) for k, v in table.items() if k in _TUNABLES}
+
+
+def options_from_env(timeout: timedelta | None = None, world: int = 0) -> "_C.Options":
+    """Build backend options: defaults, then the measured table for this world
+    size, then the FAIRRING_* environment variables."""
     opts = _C.Options(timeout) if timeout is not None else _C.Options()
+    for key, value in tuning_table(world).items():
+        if _TUNABLES[key] not in os.environ:
+            setattr(opts, key, value)
     if "FAIRRING_TOTAL_MEMORY" not in os.environ:
         sys.stderr.write(
             "The Fairring process group will allocate up to 50 MiB of staging memory "
@@ -124,6 +166,10 @@ def options_from_env(timeout: timedelta | None = None) -> "_C.Options":
     opts.blocks = _env_int("FAIRRING_BLOCKS", opts.blocks)
     opts.sm_budget = _env_int("FAIRRING_SM_BUDGET", opts.sm_budget)
     opts.oneshot_max_bytes = _env_int("FAIRRING_ONESHOT_MAX", opts.oneshot_max_bytes)
+    opts.ll_max_bytes = _env_int("FAIRRING_LL_MAX", opts.ll_max_bytes)
+    opts.ll_channels = _env_int("FAIRRING_LL_CHANNELS", opts.ll_channels)
+    opts.inline_small = os.environ.get("FAIRRING_INLINE_SMALL", "1") == "1"
+    opts.direct_unroll = _env_int("FAIRRING_DIRECT_UNROLL", opts.direct_unroll)
     opts.nvls_min_bytes = _env_int("FAIRRING_NVLS_MIN", opts.nvls_min_bytes)
     opts.nvls_oneshot_max_bytes = _env_int("FAIRRING_NVLS_ONESHOT_MAX", opts.nvls_oneshot_max_bytes)
     opts.device_timeout_ms = _env_int("FAIRRING_DEVICE_TIMEOUT_MS", opts.device_timeout_ms)
@@ -161,7 +207,7 @@ def _delegate_factory(store, rank: int, size: int, timeout: timedelta):
 
 def create_process_group_fairring(store, rank, size, timeout):
     """Factory registered with torch.distributed (fairring/__init__.py:17-46 in the reference)."""
-    backend = _C.Backend(store, rank, size, options_from_env(timeout))
+    backend = _C.Backend(store, rank, size, options_from_env(timeout, world=size))
     backend.set_delegate_factory(_delegate_factory(store, rank, size, timeout))
     return backend
 

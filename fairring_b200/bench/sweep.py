@@ -5,6 +5,11 @@ Run one process per GPU, e.g.
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \\
         --master-port 29500 -m fairring_b200.bench.sweep --min-bytes 4096 --max-bytes 1073741824
 
+Backends (``--backends``): ``fairring``; ``nccl`` (ordinary memory);
+``nccl_reg`` (NCCL on memory from its own registered allocator, the fair
+counterpart of ``--symmetric``); ``refseq`` (the reference's per-slice NCCL
+sequence, see ``fairring_b200.bench.refseq``).
+
 Contiguous fp32 and bf16 buffers, values N(0,1) seeded per rank, sizes in
 powers of two.  Every time is measured on the device with CUDA events around a
 train of back-to-back calls, each on a different slice of an arena larger than
@@ -54,9 +59,25 @@ def main(argv=None) -> int:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("fairring", rank=rank, world_size=world)
+    side = dist.new_group(backend="gloo")  # the harness's own bookkeeping
     groups = {}
+    nccl_group = None
+    refseq = None
     for b in args.backends.split(","):
-        groups[b] = dist.group.WORLD if b == "fairring" else dist.new_group(backend=b)
+        if b == "fairring":
+            groups[b] = dist.group.WORLD
+        elif b in ("nccl", "nccl_reg"):
+            nccl_group = nccl_group or dist.new_group(backend="nccl")
+            groups[b] = nccl_group
+        elif b == "refseq":
+            from .refseq import ReferenceSequence
+
+            gpm = int(os.environ.get("FAIRRING_GPUS_PER_MACHINE", "0")) or world
+            refseq = ReferenceSequence(world, rank, gpm, dev,
+                                       favorable=os.environ.get("FAIRRING_RANK_LAYOUT", "standard") == "favorable")
+            groups[b] = None
+        else:
+            raise SystemExit(f"unknown backend {b}")
 
     arena_bytes = max(args.arena_bytes, args.max_bytes)
     rows = []
@@ -69,6 +90,17 @@ def main(argv=None) -> int:
         if args.symmetric and "fairring" in groups:
             sym_arena = fairring_b200.get_backend(device="cuda").symmetric_empty(arena.numel(), dtype)
             sym_arena.copy_(arena)
+        reg_arena, reg_note = None, ""
+        if "nccl_reg" in groups:
+            try:
+                nccl_be = nccl_group._get_backend(dev)
+                pool = torch.cuda.MemPool(nccl_be.mem_allocator)
+                with torch.cuda.use_mem_pool(pool):
+                    reg_arena = torch.empty(arena.numel(), device=dev, dtype=dtype)
+                reg_arena.copy_(arena)
+                nccl_be.register_mem_pool(pool)
+            except Exception as e:  # noqa: BLE001
+                reg_arena, reg_note = None, f"unavailable: {str(e)[:160]}"
         size = args.min_bytes
         while size <= args.max_bytes:
             n = size // es
@@ -76,19 +108,27 @@ def main(argv=None) -> int:
             iters = 200 if size <= (1 << 20) else (40 if size <= (64 << 20) else 10)
             for bname, group in groups.items():
                 buf = sym_arena if (bname == "fairring" and sym_arena is not None) else arena
+                if bname == "nccl_reg":
+                    if reg_arena is None:
+                        if size == args.min_bytes:
+                            rows.append({"backend": bname, "dtype": dname, "note": reg_note})
+                        continue
+                    buf = reg_arena
 
-                def call(i, n=n, slots=slots, group=group, buf=buf):
+                def call(i, n=n, slots=slots, group=group, buf=buf, bname=bname):
                     j = i % slots
-                    dist.all_reduce(buf[j * n:(j + 1) * n], group=group)
+                    if bname == "refseq":
+                        refseq.all_reduce(buf[j * n:(j + 1) * n])
+                    else:
+                        dist.all_reduce(buf[j * n:(j + 1) * n], group=group)
 
                 for i in range(5):
                     call(i)
                 torch.cuda.synchronize()
-                dist.barrier(group=group)
-                torch.cuda.synchronize()
+                dist.barrier(group=side)
                 us = _time_train(call, iters)
-                t = torch.tensor([us], dtype=torch.float64, device=dev)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+                t = torch.tensor([us], dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=side)
                 us = float(t.item())
                 busbw = 2 * (world - 1) / world * size / (us * 1e-6) / 1e9 if world > 1 else 0.0
                 rows.append({"backend": bname + ("(symmetric)" if buf is sym_arena and sym_arena is not None else ""),
@@ -111,16 +151,18 @@ def main(argv=None) -> int:
         print(f"{'dtype':6} {'bytes':>12} " + " ".join(f"{b + ' us':>14} {b + ' busGB/s':>16}" for b in groups))
         by = {}
         for r in rows:
-            by.setdefault((r["dtype"], r["bytes"]), {})[r["backend"].split("(")[0]] = r
+            if "bytes" in r:
+                by.setdefault((r["dtype"], r["bytes"]), {})[r["backend"].split("(")[0]] = r
         for (dname, size), d in by.items():
             print(f"{dname:6} {size:12d} " + " ".join(
-                f"{d[b]['us']:14.2f} {d[b]['busbw_gbs']:16.2f}" for b in groups))
+                f"{d[b]['us']:14.2f} {d[b]['busbw_gbs']:16.2f}" if b in d else f"{'-':>14} {'-':>16}"
+                for b in groups))
         for r in rows:
             print(json.dumps(r))
         if args.json:
             with open(args.json, "w") as f:
                 json.dump({"describe": be.describe(), "rows": rows}, f, indent=1)
-    dist.barrier()
+    dist.barrier(group=side)
     dist.destroy_process_group()
     return 0
 

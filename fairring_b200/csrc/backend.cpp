@@ -259,6 +259,10 @@ std::shared_ptr<Engine> BackendFairring::ensureEngine(int device) {
   cfg.blocks = (int32_t)options_->blocks;
   cfg.sm_budget = (int32_t)options_->sm_budget;
   cfg.oneshot_max_bytes = options_->oneshot_max_bytes;
+  cfg.ll_max_bytes = options_->ll_max_bytes;
+  cfg.ll_channels = (int32_t)options_->ll_channels;
+  cfg.inline_small = options_->inline_small;
+  cfg.direct_unroll = (int32_t)options_->direct_unroll;
   cfg.nvls_min_bytes = options_->nvls_min_bytes;
   cfg.nvls_oneshot_max_bytes = options_->nvls_oneshot_max_bytes;
   const int64_t wait_ms = options_->device_timeout_ms > 0 ? options_->device_timeout_ms
@@ -442,6 +446,19 @@ c10::intrusive_ptr<c10d::Work> BackendFairring::allreduce(std::vector<at::Tensor
   d.io = d.wire = m.dtype;
   d.op = m.op;
   d.scale = m.scale;
+  if (!opts.asyncOp && engine_->fitsInline(d)) {
+    // A small blocking all_reduce: the kernel goes on the caller's own stream,
+    // which would wait for it anyway; nothing is handed to a side stream.
+    const c10::DeviceIndex di = static_cast<c10::DeviceIndex>(engine_device_);
+    c10::cuda::CUDAGuard guard(di);
+    try {
+      engine_->runInline(d, c10::cuda::getCurrentCUDAStream(di).stream());
+    } catch (const Error& e) {
+      TORCH_CHECK(false, e.what());
+    }
+    ++seq_;
+    return completedWork(c10d::OpType::ALLREDUCE, tensors);
+  }
   return runGpu(c10d::OpType::ALLREDUCE, d, {t}, tensors, nullptr);
 }
 
@@ -753,6 +770,7 @@ std::map<std::string, int64_t> BackendFairring::stats() {
     m["gpu_collectives"] = (int64_t)s.collectives;
     m["gpu_slices"] = (int64_t)s.slices;
     m["gpu_wire_bytes"] = (int64_t)s.wire_bytes;
+    m["gpu_inline_collectives"] = (int64_t)s.inline_collectives;
     m["symmetric_regions"] = (int64_t)s.symmetric_regions;
     m["symmetric_bytes"] = (int64_t)s.symmetric_bytes;
     m["symmetric_pending_release"] = (int64_t)s.symmetric_pending;
@@ -840,6 +858,20 @@ int64_t BackendFairring::releaseSymmetric() {
   if (!e) return 0;
   try {
     return e->releaseFreedSymmetric();
+  } catch (const Error& err) {
+    TORCH_CHECK(false, err.what());
+  }
+}
+
+void BackendFairring::setOption(const std::string& name, int64_t value) {
+  std::shared_ptr<Engine> e;
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    e = engine_;
+  }
+  TORCH_CHECK(e, "fairring: no GPU engine yet (run a collective first)");
+  try {
+    e->setOption(name, value);
   } catch (const Error& err) {
     TORCH_CHECK(false, err.what());
   }

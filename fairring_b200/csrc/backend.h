@@ -48,6 +48,10 @@ struct OptionsFairring : c10d::Backend::Options {
   int64_t blocks = 16;
   int64_t sm_budget = 64;
   int64_t oneshot_max_bytes = 256 << 10;
+  int64_t ll_max_bytes = 32 << 10;   // flag-in-data kernel up to this size; 0: off
+  int64_t ll_channels = 4;
+  bool inline_small = true;          // blocking small all_reduce runs on the caller's stream
+  int64_t direct_unroll = 8;
   int64_t nvls_min_bytes = 0;
   int64_t nvls_oneshot_max_bytes = 2 << 20;
   // Limit of one device-side wait on a peer.  0: the process group's timeout,
@@ -198,6 +202,9 @@ class BackendFairring : public c10d::Backend {
   // Host-side look at the kernels' status words, without synchronising: empty
   // when healthy, else what gave up waiting for whom.
   std::string health();
+  // Collective in spirit: every rank changes the same engine tunable at the same
+  // point between collectives (used by the tuning sweep).
+  void setOption(const std::string& name, int64_t value);
   void reset();
   // Collective: unmap the symmetric tensors that have died on every rank.
   int64_t releaseSymmetric();

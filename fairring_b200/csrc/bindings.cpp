@@ -44,6 +44,7 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedPipeAllreduce(
     std::vector<at::Tensor> inputs, const std::string& op, double scale, int64_t blocks,
     int64_t chunk_bytes, int64_t slot_bytes, int64_t slots, int64_t stage_bytes, int64_t stages,
     int64_t timeout_ms, int64_t silent_rank, int64_t repeats);
+double lastEmulatedUs();
 }
 
 template <typename T>
@@ -70,6 +71,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("blocks", &OptionsFairring::blocks)
       .def_readwrite("sm_budget", &OptionsFairring::sm_budget)
       .def_readwrite("oneshot_max_bytes", &OptionsFairring::oneshot_max_bytes)
+      .def_readwrite("ll_max_bytes", &OptionsFairring::ll_max_bytes)
+      .def_readwrite("ll_channels", &OptionsFairring::ll_channels)
+      .def_readwrite("inline_small", &OptionsFairring::inline_small)
+      .def_readwrite("direct_unroll", &OptionsFairring::direct_unroll)
       .def_readwrite("nvls_min_bytes", &OptionsFairring::nvls_min_bytes)
       .def_readwrite("nvls_oneshot_max_bytes", &OptionsFairring::nvls_oneshot_max_bytes)
       .def_readwrite("device_timeout_ms", &OptionsFairring::device_timeout_ms)
@@ -128,6 +133,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("trace", &BackendFairring::trace, py::call_guard<py::gil_scoped_release>())
       .def("check_health", &BackendFairring::checkHealth, py::call_guard<py::gil_scoped_release>())
       .def("health", &BackendFairring::health, py::call_guard<py::gil_scoped_release>())
+      .def("set_option", &BackendFairring::setOption, py::arg("name"), py::arg("value"),
+           py::call_guard<py::gil_scoped_release>())
       .def("release_symmetric", &BackendFairring::releaseSymmetric,
            py::call_guard<py::gil_scoped_release>())
       .def("reset", &BackendFairring::reset, py::call_guard<py::gil_scoped_release>())
@@ -216,6 +223,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("stages") = 4, py::arg("timeout_ms") = 2000, py::arg("silent_rank") = -1,
         py::arg("repeats") = 1);
 
+  m.def("last_emulated_us", &lastEmulatedUs);
   m.def("launch_count", []() { return (int64_t)(launchCount() + localLaunchCount()); });
   m.def("collective_launch_count", []() { return (int64_t)launchCount(); });
   m.attr("MAX_RANKS") = kMaxRanks;

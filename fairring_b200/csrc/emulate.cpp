@@ -9,6 +9,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 
+#include <cstdlib>
 #include <tuple>
 #include <vector>
 
@@ -72,8 +73,11 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
   auto bopt = inputs[0].options();
   auto u8 = bopt.dtype(at::kByte);
   auto i32 = bopt.dtype(at::kInt);
-  std::vector<at::Tensor> staging, flags, seqs, outs;
+  std::vector<at::Tensor> staging, flags, seqs, outs, lls;
+  // flag-in-data areas: two halves of [rank][unit] 16-byte words
+  const int64_t ll_half = (int64_t)kMaxRanks * roundUp(ceilDiv(algo == "ll" ? n_in * dtypeSize(io) : 8, 8), 64) * 16;
   for (int r = 0; r < W; ++r) {
+    lls.push_back(at::zeros({2 * ll_half}, u8));
     staging.push_back(at::zeros({2 * half_bytes}, u8));
     flags.push_back(at::zeros({kMaxRanks * kMaxBlocks}, i32));
     seqs.push_back(at::zeros({kMaxBlocks}, i32));
@@ -82,6 +86,7 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
     else outs.push_back(at::zeros({per_rank * W}, bopt));
   }
   at::Tensor scratch = at::zeros({kMaxRanks * kMaxBlocks}, i32);
+  at::Tensor ll_scratch = at::zeros({2 * ll_half}, u8);
   uint32_t* status_host = nullptr;
   FR_CUDA(cudaHostAlloc((void**)&status_host, sizeof(uint32_t) * (W * kStatusWords + 1),
                         cudaHostAllocMapped));
@@ -96,8 +101,13 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
     for (int p = 0; p < W; ++p) {
       c.staging[p] = static_cast<char*>(staging[p].data_ptr());
       c.flags[p] = static_cast<uint32_t*>(flags[p].data_ptr());
-      if (r == silent_rank && p != r) c.flags[p] = static_cast<uint32_t*>(scratch.data_ptr());
+      c.ll[p] = static_cast<char*>(lls[p].data_ptr());
+      if (r == silent_rank && p != r) {
+        c.flags[p] = static_cast<uint32_t*>(scratch.data_ptr());
+        c.ll[p] = static_cast<char*>(ll_scratch.data_ptr());
+      }
     }
+    c.ll_half_bytes = (uint64_t)ll_half;
     c.mc_staging = nullptr;
     c.seq = static_cast<uint32_t*>(seqs[r].data_ptr());
     c.status = status_dev + r * kStatusWords;
@@ -153,6 +163,9 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
                                        static_cast<const ChannelDev*>(chs_dev.data_ptr()), a, W,
                                        (int)blocks, stream);
         TORCH_CHECK(e == cudaSuccess, "emulated direct launch failed: ", cudaGetErrorString(e));
+      } else if (algo == "ll") {
+        TORCH_CHECK(io == wire, "the flag-in-data kernel carries the tensor's own dtype");
+        launchAll(KernelId::LL_ONESHOT, allreduceSeg(n_in, wes, W), 0, 0, kAdvanceSeq);
       } else if (algo == "oneshot") {
         const Seg s = allreduceSeg(n_in, wes, W);
         TORCH_CHECK((int64_t)W * W * s.qv * kVecBytes <= half_bytes, "message too large for one-shot");
@@ -199,6 +212,11 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
   cudaFreeHost(status_host);
   return std::make_tuple(outs, status);
 }
+
+// Device time per launch of the last emulatedPipeAllreduce call (CUDA events
+// around the launches only), for kernel timing on one GPU.
+static double g_last_emulated_us = 0;
+double lastEmulatedUs() { return g_last_emulated_us; }
 
 // The pipelined all-reduce (kernels/pipe_allreduce.h) with all ranks on one GPU,
 // peer-load flavour.  Every launch all-reduces the inputs in place; `repeats`
@@ -279,13 +297,24 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedPipeAllreduce(
   a.nvls = 0;
   a.stage_bytes = (int32_t)stage_bytes;
   a.stages = (int32_t)stages;
+  if (const char* dbg = std::getenv("FR_PIPE_DEBUG")) a.debug = std::atoi(dbg);
+  cudaEvent_t t0, t1;
+  FR_CUDA(cudaEventCreate(&t0));
+  FR_CUDA(cudaEventCreate(&t1));
+  FR_CUDA(cudaEventRecord(t0, stream));
   for (int64_t rep = 0; rep < repeats; ++rep) {
     cudaError_t e = launchPipeEmulated(static_cast<const PipeChannelDev*>(chs_dev.data_ptr()), a, W,
                                        (int)blocks, stream);
     TORCH_CHECK(e == cudaSuccess, "emulated launch of pipe_allreduce failed: ",
                 cudaGetErrorString(e));
   }
+  FR_CUDA(cudaEventRecord(t1, stream));
   FR_CUDA(cudaStreamSynchronize(stream));
+  float ms = 0;
+  cudaEventElapsedTime(&ms, t0, t1);
+  g_last_emulated_us = (double)ms * 1e3 / (double)std::max<int64_t>(1, repeats);
+  cudaEventDestroy(t0);
+  cudaEventDestroy(t1);
   at::Tensor status = at::zeros({W, kStatusWords}, at::kInt);
   std::memcpy(status.data_ptr(), status_host, sizeof(uint32_t) * W * kStatusWords);
   cudaFreeHost(status_host);

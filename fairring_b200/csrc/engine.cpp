@@ -22,16 +22,17 @@ const char* algoName(Algo a) {
     case Algo::NVLS: return "nvls";
     case Algo::NVLS_ONESHOT: return "nvls_oneshot";
     case Algo::PIPE: return "pipe";
+    case Algo::LL: return "ll";
   }
   return "?";
 }
 
 Algo parseAlgo(const std::string& s) {
   for (Algo a : {Algo::AUTO, Algo::ONESHOT, Algo::TWOSHOT, Algo::HIER, Algo::NVLS, Algo::NVLS_ONESHOT,
-                 Algo::PIPE})
+                 Algo::PIPE, Algo::LL})
     if (s == algoName(a)) return a;
   FR_CHECK(false, "unknown FAIRRING_ALGO '", s,
-           "' (auto, oneshot, twoshot, hier, nvls, nvls_oneshot, pipe)");
+           "' (auto, oneshot, twoshot, hier, nvls, nvls_oneshot, pipe, ll)");
   return Algo::AUTO;
 }
 
@@ -74,6 +75,7 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
   // also takes most of the shared memory).
   int sms = 0;
   FR_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_));
+  sm_count_ = sms;
   const bool want_pipe = cfg_.pipe != "off" && topo_.world > 1 && topo_.M == 1;
   if (cfg_.pipe_blocks < 1) cfg_.pipe_blocks = 1;
   if (cfg_.pipe_blocks > kMaxBlocks) cfg_.pipe_blocks = kMaxBlocks;
@@ -83,10 +85,23 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
   const int budget = std::max(widest, std::min(sms, cfg_.sm_budget));
   const int max_channels = std::max(1, budget / widest);
   if (cfg_.parallelism > max_channels) cfg_.parallelism = max_channels;
-  // With the pipelined kernel the budget is cut in three: two thirds for the
+  // The flag-in-data areas come off the top of the budget (an eighth at most).
+  int64_t ll_total = 0;
+  if (cfg_.ll_max_bytes > 0 && topo_.world > 1) {
+    ll_channels_ = std::max(1, std::min(cfg_.ll_channels, cfg_.parallelism));
+    ll_half_bytes_ = (int64_t)kMaxRanks * roundUp(ceilDiv(cfg_.ll_max_bytes, 8), 64) * 16;
+    while (ll_channels_ > 1 && 2 * ll_half_bytes_ * ll_channels_ > cfg_.total_memory / 8) --ll_channels_;
+    if (2 * ll_half_bytes_ * ll_channels_ > cfg_.total_memory / 8) {
+      ll_channels_ = 0;
+      ll_half_bytes_ = 0;
+    }
+    ll_total = 2 * ll_half_bytes_ * ll_channels_;
+  }
+  const int64_t rest = cfg_.total_memory - ll_total;
+  // With the pipelined kernel the rest is cut in three: two thirds for the
   // staging slots of the channels, one third for its rings.
-  plan_ = planMemory(want_pipe ? cfg_.total_memory / 3 * 2 : cfg_.total_memory, cfg_.slice_bytes,
-                     cfg_.parallelism, topo_.world, cfg_.min_half_bytes);
+  plan_ = planMemory(want_pipe ? rest / 3 * 2 : rest, cfg_.slice_bytes, cfg_.parallelism,
+                     topo_.world, cfg_.min_half_bytes);
 
   alloc_.reset(new SymmAllocator(store_, topo_.rank, topo_.world, device_, cfg_.transport,
                                  cfg_.nvls, cfg_.bootstrap_timeout));
@@ -97,7 +112,7 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
   if (want_pipe) {
     pipe_channels_ = std::max(1, std::min<int>(cfg_.pipe_channels, plan_.channels));
     if (cfg_.pipe_slots < 2) cfg_.pipe_slots = 2;
-    const int64_t ring_total = cfg_.total_memory / 3;
+    const int64_t ring_total = rest / 3;
     pipe_slot_bytes_ = roundDown(ring_total / pipe_channels_ / cfg_.pipe_slots, 4096);
     if (pipe_slot_bytes_ > (8ll << 20)) pipe_slot_bytes_ = 8ll << 20;
     if (pipe_slot_bytes_ < 4096) {
@@ -111,6 +126,10 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
       FR_CUDA(cudaMemset(pipe_seq_dev_, 0, sizeof(uint32_t) * kMaxBlocks * pipe_channels_));
     }
   }
+
+  if (ll_channels_ > plan_.channels) ll_channels_ = plan_.channels;
+  if (ll_channels_ > 0)
+    ll_region_ = alloc_->allocate((size_t)(2 * ll_half_bytes_) * ll_channels_, /*want_multicast=*/false);
 
   FR_CUDA(cudaMalloc(&seq_dev_, sizeof(uint32_t) * kMaxBlocks * plan_.channels));
   FR_CUDA(cudaMemset(seq_dev_, 0, sizeof(uint32_t) * kMaxBlocks * plan_.channels));
@@ -128,11 +147,17 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
     FR_CUDA(cudaStreamCreateWithPriority(&ch.stream, cudaStreamNonBlocking,
                                          cfg_.high_priority ? hi : lo));
     FR_CUDA(cudaEventCreateWithFlags(&ch.done, cudaEventDisableTiming));
+    FR_CUDA(cudaEventCreateWithFlags(&ch.last_done, cudaEventDisableTiming));
+    ch.last_stream = ch.stream;
     for (int r = 0; r < topo_.world; ++r) {
       char* base = static_cast<char*>(region_.ptrs[r]);
       ch.dev.flags[r] = reinterpret_cast<uint32_t*>(base + kFlagPadBytes * c);
       ch.dev.staging[r] = base + flags_bytes_ + (size_t)plan_.slot_bytes * c;
+      ch.dev.ll[r] = c < ll_channels_ ? static_cast<char*>(ll_region_.ptrs[r]) +
+                                            (size_t)(2 * ll_half_bytes_) * c
+                                      : nullptr;
     }
+    ch.dev.ll_half_bytes = (uint64_t)ll_half_bytes_;
     ch.dev.mc_staging = region_.mc_ptr
                             ? static_cast<char*>(region_.mc_ptr) + flags_bytes_ +
                                   (size_t)plan_.slot_bytes * c
@@ -201,6 +226,7 @@ Engine::~Engine() {
   try {
     for (auto& kv : user_regions_) alloc_->release(kv.second.reg);
     alloc_->release(pipe_region_);
+    alloc_->release(ll_region_);
     alloc_->release(region_);
   } catch (const std::exception&) {
   }
@@ -212,6 +238,7 @@ Engine::~Engine() {
     // an exception from inside a destructor.  (The reference leaks its merge
     // streams for the same reason, fairring/machine.cc:162-175.)
     if (ch.done) cudaEventDestroy(ch.done);
+    if (ch.last_done) cudaEventDestroy(ch.last_done);
   }
   for (auto& e : free_events_)
     if (e) cudaEventDestroy(e);
@@ -303,6 +330,14 @@ void Engine::reset() {
   // start the round-robin over channels from the same place everywhere.
   next_channel_ = 0;
   next_pipe_ = 0;
+  next_ll_ = 0;
+  // (The flag-in-data areas need no clearing: sequence numbers restart at 0, and
+  // a word only counts when it carries the number of the collective that reads
+  // it; clear them anyway so that an old word cannot match a restarted count.)
+  if (ll_channels_ > 0) {
+    FR_CUDA(cudaMemset(ll_region_.ptrs[topo_.rank], 0, (size_t)(2 * ll_half_bytes_) * ll_channels_));
+    FR_CUDA(cudaDeviceSynchronize());
+  }
   store_->barrier(pfx + "/clean", topo_.world, cfg_.bootstrap_timeout);
 }
 
@@ -424,6 +459,7 @@ bool Engine::runDirect(const CollectiveDesc& d, const std::function<Channel&(int
     a.io_dtype = (int32_t)d.io;
     a.wire_dtype = (int32_t)d.wire;
     a.flags = kAdvanceSeq;
+    a.unroll = cfg_.direct_unroll;
     const size_t o = off + (size_t)start * es;
     for (int r = 0; r < W; ++r) a.peer[r] = static_cast<char*>(reg->ptrs[r]) + o;
     a.mc = nvls ? static_cast<char*>(reg->mc_ptr) + o : nullptr;
@@ -505,7 +541,8 @@ std::vector<cudaStream_t> Engine::streams() const {
 
 std::string Engine::describe() const {
   std::ostringstream os;
-  os << "world=" << topo_.world << " grouping=" << topo_.M << "x" << topo_.D
+  os << "ll=" << (ll_channels_ > 0 ? cfg_.ll_max_bytes : 0) << "B/" << ll_channels_ << "ch "
+     << "world=" << topo_.world << " grouping=" << topo_.M << "x" << topo_.D
      << (topo_.favorable ? " (device-major ranks)" : " (machine-major ranks)")
      << " transport=" << alloc_->describe() << " nvls=" << (nvlsAvailable() ? "yes" : "no")
      << " channels=" << plan_.channels << " half_slot=" << plan_.half_bytes
@@ -527,7 +564,7 @@ Algo Engine::chooseAllreduce(int64_t wire_bytes, DType wire, RedOp op) const {
   Algo a = cfg_.algo;
   if (a == Algo::ONESHOT && !oneshot_fits) a = Algo::AUTO;
   if ((a == Algo::NVLS || a == Algo::NVLS_ONESHOT) && !nvls_ok) a = Algo::AUTO;
-  if (a == Algo::PIPE) a = Algo::AUTO;  // this message did not qualify for the pipelined kernel
+  if (a == Algo::PIPE || a == Algo::LL) a = Algo::AUTO;  // this message did not qualify for that kernel
   if (a == Algo::TWOSHOT && topo_.M > 1) a = Algo::HIER;
   if (a != Algo::AUTO) return a;
   if (wire_bytes <= cfg_.oneshot_max_bytes && oneshot_fits) return Algo::ONESHOT;
@@ -537,6 +574,114 @@ Algo Engine::chooseAllreduce(int64_t wire_bytes, DType wire, RedOp op) const {
     if (wire_bytes >= cfg_.nvls_min_bytes) return Algo::NVLS;
   }
   return Algo::TWOSHOT;
+}
+
+bool Engine::fitsInline(const CollectiveDesc& d) const {
+  if (!cfg_.inline_small || ll_channels_ == 0 || d.kind != CollKind::ALLREDUCE || d.io != d.wire)
+    return false;
+  if (cfg_.algo != Algo::AUTO && cfg_.algo != Algo::LL) return false;
+  if (cfg_.command_thread) return false;
+  const int64_t bytes = d.numel * dtypeSize(d.wire);
+  return bytes > 0 && bytes <= cfg_.ll_max_bytes;
+}
+
+void Engine::launchLL(Channel& ch, const CollectiveDesc& d, cudaStream_t stream) {
+  OpArgs a{};
+  a.in[0] = d.in;
+  a.out[0] = d.out;
+  a.seg = allreduceSeg(d.numel, dtypeSize(d.wire), topo_.world);
+  a.scale = d.scale;
+  a.op = (int32_t)d.op;
+  a.io_dtype = a.wire_dtype = (int32_t)d.io;
+  a.flags = kAdvanceSeq;
+  // Always the channel's full grid: every block keeps its own count of the
+  // channel's collectives, so every launch on a channel must run every block.
+  cudaError_t e = launchCollective(KernelId::LL_ONESHOT, channels_dev_ + (&ch - channels_.data()), a,
+                                   cfg_.blocks, stream);
+  FR_CHECK(e == cudaSuccess, "launch of ll_allreduce failed: ", cudaGetErrorString(e));
+  ++stats_.launches[(size_t)KernelId::LL_ONESHOT];
+  if (cur_.launches == 0) cur_.first_kernel = (int32_t)KernelId::LL_ONESHOT;
+  ++cur_.launches;
+  ++stats_.slices;
+  stats_.wire_bytes += (uint64_t)(d.numel * dtypeSize(d.wire));
+}
+
+// A channel's kernels must run one after the other (they share its sequence
+// number, flags and areas).  On the channel's own stream that is stream order;
+// a kernel launched on a caller's stream is tied in with two events.
+void Engine::runInline(const CollectiveDesc& d, cudaStream_t caller) {
+  std::lock_guard<std::mutex> lk(mu_);
+  checkHealth();
+  Channel& ch = channels_[(size_t)(next_ll_++ % (uint64_t)ll_channels_)];
+  cur_ = TraceEntry{};
+  cur_.seq = stats_.collectives;
+  cur_.kind = (int32_t)d.kind;
+  cur_.bytes = d.numel * dtypeSize(d.wire);
+  if (ch.last_stream != caller) FR_CUDA(cudaStreamWaitEvent(caller, ch.last_done, 0));
+  launchLL(ch, d, caller);
+  FR_CUDA(cudaEventRecord(ch.last_done, caller));
+  ch.last_stream = caller;
+  cur_.slices = 1;
+  cur_.channels = 0;
+  if (trace_.size() < kTraceLen) trace_.resize(kTraceLen);
+  trace_[cur_.seq % kTraceLen] = cur_;
+  ++stats_.collectives;
+  ++stats_.inline_collectives;
+}
+
+void Engine::setOption(const std::string& name, int64_t v) {
+  std::lock_guard<std::mutex> lk(mu_);
+  const int nch = (int)channels_.size();
+  if (name == "blocks") {
+    FR_CHECK(v >= 1 && v <= kMaxBlocks && v * nch <= sm_count_, "blocks x channels exceeds the SM count");
+    // Blocks that did not run so far have a stale count of the channel's
+    // collectives: give every block the count of block 0.
+    FR_CUDA(cudaSetDevice(device_));
+    FR_CUDA(cudaDeviceSynchronize());
+    std::vector<uint32_t> seq((size_t)kMaxBlocks * nch);
+    FR_CUDA(cudaMemcpy(seq.data(), seq_dev_, seq.size() * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    for (int c = 0; c < nch; ++c)
+      for (int b = 1; b < kMaxBlocks; ++b) seq[(size_t)c * kMaxBlocks + b] = seq[(size_t)c * kMaxBlocks];
+    FR_CUDA(cudaMemcpy(seq_dev_, seq.data(), seq.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
+    cfg_.blocks = (int32_t)v;
+  } else if (name == "pipe_blocks") {
+    FR_CHECK(v >= 1 && v <= kMaxBlocks && v * pipe_channels_ + (int64_t)cfg_.blocks * (nch - pipe_channels_) <= sm_count_,
+             "pipe_blocks exceeds the SM count");
+    cfg_.pipe_blocks = (int32_t)v;
+  } else if (name == "pipe_chunk_bytes") {
+    cfg_.pipe_chunk_bytes = v;
+  } else if (name == "pipe_min_bytes") {
+    cfg_.pipe_min_bytes = v;
+  } else if (name == "pipe_stage_bytes") {
+    FR_CHECK(v >= 16 && v % 16 == 0 && pipeSharedBytes((int)v, cfg_.pipe_stages) <= (200u << 10), "stage too large");
+    cfg_.pipe_stage_bytes = (int32_t)v;
+  } else if (name == "pipe_stages") {
+    FR_CHECK(v >= 2 && v <= 8 && pipeSharedBytes(cfg_.pipe_stage_bytes, (int)v) <= (200u << 10), "too many stages");
+    cfg_.pipe_stages = (int32_t)v;
+  } else if (name == "direct_unroll") {
+    cfg_.direct_unroll = (int32_t)v;
+  } else if (name == "direct_max_slices") {
+    cfg_.direct_max_slices = (int32_t)std::max<int64_t>(1, v);
+  } else if (name == "direct_min_slice_bytes") {
+    cfg_.direct_min_slice_bytes = std::max<int64_t>(kVecBytes * topo_.world, v);
+  } else if (name == "ll_max_bytes") {
+    FR_CHECK(ll_channels_ == 0 || (int64_t)kMaxRanks * roundUp(ceilDiv(v, 8), 64) * 16 <= ll_half_bytes_,
+             "ll_max_bytes beyond the areas allocated at start-up");
+    cfg_.ll_max_bytes = v;
+  } else if (name == "oneshot_max_bytes") {
+    cfg_.oneshot_max_bytes = v;
+  } else if (name == "nvls_oneshot_max_bytes") {
+    cfg_.nvls_oneshot_max_bytes = v;
+  } else if (name == "nvls_min_bytes") {
+    cfg_.nvls_min_bytes = v;
+  } else if (name == "inline_small") {
+    cfg_.inline_small = v != 0;
+  } else if (name == "algo") {
+    FR_CHECK(v >= 0 && v <= (int64_t)Algo::LL, "algo out of range");
+    cfg_.algo = (Algo)v;
+  } else {
+    FR_CHECK(false, "unknown engine option '", name, "'");
+  }
 }
 
 void Engine::launch(Channel& ch, KernelId id, const OpArgs& a) {
@@ -599,7 +744,12 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after,
   std::function<Channel&(int)> take = [&](int want) -> Channel& {
     const int c = want >= 0 ? want : (int)(next_channel_++ % channels_.size());
     if (std::find(used.begin(), used.end(), c) == used.end()) {
-      FR_CUDA(cudaStreamWaitEvent(channels_[c].stream, after, 0));
+      Channel& ch = channels_[c];
+      FR_CUDA(cudaStreamWaitEvent(ch.stream, after, 0));
+      if (ch.last_stream != ch.stream) {  // its last kernel ran inline on a caller's stream
+        FR_CUDA(cudaStreamWaitEvent(ch.stream, ch.last_done, 0));
+        ch.last_stream = ch.stream;
+      }
       used.push_back(c);
     }
     return channels_[c];
@@ -634,7 +784,13 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after,
     }
   } finish{this, &used, t_begin, slices_before};
 
-  if (runDirect(d, take) || runPipe(d, take)) {
+  const bool ll_fits = ll_channels_ > 0 && d.kind == CollKind::ALLREDUCE && d.io == d.wire &&
+                       d.numel > 0 && d.numel * wes <= cfg_.ll_max_bytes &&
+                       (cfg_.algo == Algo::AUTO || cfg_.algo == Algo::LL);
+  if (ll_fits) {
+    Channel& ch = take((int)(next_ll_++ % (uint64_t)ll_channels_));
+    launchLL(ch, d, ch.stream);
+  } else if (runDirect(d, take) || runPipe(d, take)) {
     // nothing else to do
   } else if (d.kind == CollKind::ALLREDUCE) {
     const int64_t bytes = d.numel * wes;
@@ -704,6 +860,12 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after,
     Channel& ch = take(-1);
     return ch.stream;
   }
+  if (cfg_.inline_small)
+    for (int c : used)
+      if (c < ll_channels_) {  // an inline collective may come next on this channel
+        FR_CUDA(cudaEventRecord(channels_[c].last_done, channels_[c].stream));
+        channels_[c].last_stream = channels_[c].stream;
+      }
   if (used_streams)
     for (int c : used) used_streams->push_back(channels_[c].stream);
   Channel& join = channels_[used[0]];

@@ -31,7 +31,7 @@
 
 namespace fairring {
 
-enum class Algo : int32_t { AUTO = 0, ONESHOT, TWOSHOT, HIER, NVLS, NVLS_ONESHOT, PIPE };
+enum class Algo : int32_t { AUTO = 0, ONESHOT, TWOSHOT, HIER, NVLS, NVLS_ONESHOT, PIPE, LL };
 const char* algoName(Algo a);
 Algo parseAlgo(const std::string& s);
 
@@ -43,6 +43,15 @@ struct EngineConfig {
   int32_t blocks = 16;                 // thread blocks per kernel
   int32_t sm_budget = 64;              // channels x blocks never exceeds this (nor the SM count)
   int64_t oneshot_max_bytes = 256 << 10;
+  // Messages up to ll_max_bytes take the flag-in-data kernel (no barrier at
+  // all); its areas (2 x 16 bytes per 8 bytes of message per rank, on up to
+  // ll_channels channels) come off the top of the memory budget.  0: off.
+  int64_t ll_max_bytes = 32 << 10;
+  int32_t ll_channels = 4;
+  // A blocking all_reduce (async_op=False) that fits the flag-in-data kernel is
+  // launched on the caller's own stream: no hand-over to a side stream and back.
+  bool inline_small = true;
+  int32_t direct_unroll = 8;           // in-place NVLS kernel: 16-byte loads in flight per thread
   int64_t nvls_min_bytes = 0;          // below this the peer-load two-shot is used
   int64_t nvls_oneshot_max_bytes = 2 << 20;
   uint64_t device_timeout_ns = 30ull * 1000 * 1000 * 1000;
@@ -88,6 +97,7 @@ struct EngineStats {
   uint64_t collectives = 0;
   uint64_t slices = 0;
   uint64_t wire_bytes = 0;
+  uint64_t inline_collectives = 0;  // launched on the caller's stream
   uint64_t symmetric_regions = 0;   // live allocations handed out by allocSymmetric
   uint64_t symmetric_bytes = 0;     // ... and their size (outside the staging budget)
   uint64_t symmetric_pending = 0;   // freed by their tensor, not yet released by all ranks
@@ -136,6 +146,15 @@ class Engine {
   // `used` (optional) receives every side stream the collective touched.
   cudaStream_t run(const CollectiveDesc& d, cudaEvent_t after,
                    std::vector<cudaStream_t>* used_streams = nullptr);
+  // Would run() put this collective on the caller's stream if asked to?
+  bool fitsInline(const CollectiveDesc& d) const;
+  // The same collective launched on `caller` itself (see inline_small).  Only
+  // for descriptors for which fitsInline() holds.
+  void runInline(const CollectiveDesc& d, cudaStream_t caller);
+  // Changes a tunable between collectives; every rank must make the same call
+  // at the same point.  Throws for unknown names and values that would break
+  // the residency bound.
+  void setOption(const std::string& name, int64_t value);
   // Run `fn` now, or on the command thread when one is configured.
   void submit(std::function<void()> fn);
 
@@ -175,7 +194,12 @@ class Engine {
     cudaStream_t stream = nullptr;
     ChannelDev dev{};
     cudaEvent_t done = nullptr;
+    // Where the channel's last kernel was launched (its own stream, or a
+    // caller's for an inline collective) and an event recorded after it.
+    cudaStream_t last_stream = nullptr;
+    cudaEvent_t last_done = nullptr;
   };
+  void launchLL(Channel& ch, const CollectiveDesc& d, cudaStream_t stream);
   void launch(Channel& ch, KernelId id, const OpArgs& a);
   void runAllreduceSlice(Channel& ch, const CollectiveDesc& d, const void* in, void* out,
                          int64_t n, Algo algo);
@@ -205,6 +229,11 @@ class Engine {
   int64_t pipe_slot_bytes_ = 0;
   int pipe_channels_ = 0;
   uint64_t next_pipe_ = 0;
+  SymmRegion ll_region_;
+  int64_t ll_half_bytes_ = 0;
+  int ll_channels_ = 0;
+  uint64_t next_ll_ = 0;
+  int sm_count_ = 0;
   uint32_t* pipe_seq_dev_ = nullptr;
   PipeChannelDev* pipe_channels_dev_ = nullptr;
   size_t flags_bytes_ = 0;

@@ -53,6 +53,7 @@ const char* kernelName(KernelId id) {
     case KernelId::NVLS_ONESHOT: return "nvls_oneshot_allreduce";
     case KernelId::P2P_DIRECT: return "direct_allreduce";
     case KernelId::NVLS_DIRECT: return "nvls_direct_allreduce";
+    case KernelId::LL_ONESHOT: return "ll_allreduce";
     case KernelId::PIPE: return "pipe_allreduce";
     default: return "?";
   }
@@ -79,6 +80,7 @@ cudaError_t launchImpl(KernelId id, const ChannelDev* chs, const OpArgs& args, i
       !nvlsSupported((DType)args.wire_dtype, (RedOp)args.op))
     return cudaErrorInvalidValue;
   if (id == KernelId::NVLS_DIRECT && args.mc == nullptr) return cudaErrorInvalidValue;
+  if (id == KernelId::PIPE) return cudaErrorInvalidValue;  // launched through launchPipeAllreduce
   cudaError_t e;
   if (cooperative) {
     // All blocks of all emulated ranks wait on one another: they must be

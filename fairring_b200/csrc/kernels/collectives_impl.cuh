@@ -749,11 +749,10 @@ __device__ __forceinline__ void phaseDirectPeer(const ChannelDev& c, const OpArg
   FR_WITH_UNROLL(c.topo.world, 1, phaseDirectPeerU<WIRE, U, KP>(c, a, bc));
 }
 
-template <typename WIRE>
-__device__ __forceinline__ void phaseDirectNvls(const ChannelDev& c, const OpArgs& a,
-                                                const BlockCtx& bc) {
+template <typename WIRE, int U>
+__device__ __forceinline__ void phaseDirectNvlsU(const ChannelDev& c, const OpArgs& a,
+                                                 const BlockCtx& bc) {
   constexpr int V = kVecBytes / sizeof(WIRE);
-  constexpr int U = 4;
   using Acc = typename Tr<WIRE>::Acc;
   const Topo& t = c.topo;
   const Seg& s = a.seg;
@@ -782,6 +781,147 @@ __device__ __forceinline__ void phaseDirectNvls(const ChannelDev& c, const OpArg
       multimemSt(mc + (base + tb.v[u]) * kVecBytes, r[u]);
     }
   }
+}
+// a.unroll picks how many 16-byte multimem loads a thread keeps in flight.
+template <typename WIRE>
+__device__ __forceinline__ void phaseDirectNvls(const ChannelDev& c, const OpArgs& a,
+                                                const BlockCtx& bc) {
+  if (a.unroll >= 16)
+    phaseDirectNvlsU<WIRE, 16>(c, a, bc);
+  else if (a.unroll >= 8)
+    phaseDirectNvlsU<WIRE, 8>(c, a, bc);
+  else
+    phaseDirectNvlsU<WIRE, 4>(c, a, bc);
+}
+
+// ---------------------------------------------------------------------------
+// Phase: flag-in-data one-shot (small messages).  A unit is 8 bytes of the
+// message.  Every rank stores its units, scaled, into the area of every peer as
+// 16-byte words {data.lo, n, data.hi, n}, n = number of this collective on the
+// channel (never 0).  A receiver spins on the word itself until both copies of
+// n are there -- a 16-byte store may arrive as two 8-byte halves, each half then
+// carries its own copy -- and reduces in rank order, so every rank gets the same
+// bits.  No barrier and no separate flag: one trip over NVLink.
+// The area holds LL words of earlier collectives only, so an old word can never
+// be taken for a new one.  Halves alternate like the staging halves; a rank can
+// be at most one collective ahead of the slowest peer (it needs everybody's
+// words to finish), so the half written now was read two collectives ago.
+// ---------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ bool phaseLL(const ChannelDev& c, const OpArgs& a, const BlockCtx& bc) {
+  constexpr int E = 8 / sizeof(T);
+  using Acc = typename Tr<T>::Acc;
+  const Topo& t = c.topo;
+  const int W = t.world;
+  const int64_t n = a.seg.limit;
+  const int64_t units = ceilDiv(n, E);
+  const int64_t cap = (int64_t)(c.ll_half_bytes / 16 / kMaxRanks);  // units per source rank
+  const uint32_t tag = bc.seq + 1u == 0u ? 1u : bc.seq + 1u;
+  const uint64_t half = (bc.seq & 1u) ? c.ll_half_bytes : 0;
+  const T* in = static_cast<const T*>(a.in[blockIdx.y]);
+  T* out = static_cast<T*>(a.out[blockIdx.y]);
+  const bool in_al = (reinterpret_cast<uintptr_t>(in) & 7u) == 0;
+  const bool out_al = (reinterpret_cast<uintptr_t>(out) & 7u) == 0;
+  char* own = c.ll[t.rank] + half;
+
+  auto loadUnit = [&](int64_t u, Acc (&x)[E]) {
+    const int64_t e0 = u * E;
+    if (in_al && e0 + E <= n) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(in + e0);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int i = 0; i < E; ++i) x[i] = Tr<T>::up(e[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < E; ++i) x[i] = e0 + i < n ? Tr<T>::up(in[e0 + i]) : Acc(0);
+    }
+    applyScale(x, a.scale);
+  };
+  auto packUnit = [&](const Acc (&x)[E]) {
+    uint2 raw;
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < E; ++i) e[i] = Tr<T>::down(x[i]);
+    return raw;
+  };
+
+  const int64_t stride = (int64_t)bc.G * kThreads;
+  for (int64_t u = (int64_t)bc.b * kThreads + threadIdx.x; u < units; u += stride) {
+    Acc x[E];
+    loadUnit(u, x);
+    const uint2 d = packUnit(x);
+    const uint4 word = make_uint4(d.x, tag, d.y, tag);
+#pragma unroll
+    for (int k = 1; k < kMaxRanks; ++k)
+      if (k < W)
+        stStage(c.ll[(t.rank + k) % W] + half + ((int64_t)t.rank * cap + u) * 16, word);
+  }
+  bool ok = true;
+  for (int64_t u = (int64_t)bc.b * kThreads + threadIdx.x; ok && u < units; u += stride) {
+    Acc acc[E];
+#pragma unroll
+    for (int q = 0; q < kMaxRanks; ++q) {
+      if (q >= W) break;
+      Acc x[E];
+      if (q == t.rank) {
+        loadUnit(u, x);
+        // what the peers got: the value after the round trip through T
+        const uint2 d = packUnit(x);
+        const T* e = reinterpret_cast<const T*>(&d);
+#pragma unroll
+        for (int i = 0; i < E; ++i) x[i] = Tr<T>::up(e[i]);
+      } else {
+        const char* p = own + ((int64_t)q * cap + u) * 16;
+        uint4 w = ldStage(p);
+        if (w.y != tag || w.w != tag) {
+          uint64_t t0 = 0;
+          const uint64_t iter_cap = c.timeout_ns / 32 + (1ull << 20);
+          for (uint64_t it = 1;; ++it) {
+            w = ldStage(p);
+            if (w.y == tag && w.w == tag) break;
+            if ((it & 63) == 0) {
+              const uint64_t now = globalTimerNs();
+              if (t0 == 0) t0 = now;
+              const bool aborted = (it & 1023) == 0 && c.abort_flag != nullptr &&
+                                   ldVolatile(c.abort_flag) != 0;
+              if (now - t0 > c.timeout_ns || it > iter_cap || aborted) {
+                volatile uint32_t* st = c.status;
+                st[1] = 0;
+                st[2] = (uint32_t)q;
+                st[3] = bc.seq;
+                __threadfence_system();
+                st[0] = aborted ? kStatusAborted : kStatusTimeout;
+                ok = false;
+                break;
+              }
+            }
+          }
+          if (!ok) break;
+        }
+        const uint2 d = make_uint2(w.x, w.z);
+        const T* e = reinterpret_cast<const T*>(&d);
+#pragma unroll
+        for (int i = 0; i < E; ++i) x[i] = Tr<T>::up(e[i]);
+      }
+      if (q == 0) {
+#pragma unroll
+        for (int i = 0; i < E; ++i) acc[i] = x[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < E; ++i) acc[i] = combine(acc[i], x[i], a.op);
+      }
+    }
+    if (!ok) break;
+    const int64_t e0 = u * E;
+    if (out_al && e0 + E <= n) {
+      *reinterpret_cast<uint2*>(out + e0) = packUnit(acc);
+    } else {
+#pragma unroll
+      for (int i = 0; i < E; ++i)
+        if (e0 + i < n) out[e0 + i] = Tr<T>::down(acc[i]);
+    }
+  }
+  return ok;
 }
 
 // ---------------------------------------------------------------------------
@@ -838,6 +978,8 @@ __device__ __forceinline__ void body(const ChannelDev& c, const OpArgs& a) {
       phaseDirectNvls<WIRE>(c, a, bc);
       barrier<kAll>(c, bc, 3);
     }
+  } else if constexpr (K == KernelId::LL_ONESHOT) {
+    phaseLL<WIRE>(c, a, bc);
   }
   leave(c, a, bc);
 }
@@ -863,6 +1005,7 @@ FR_DEFINE_KERNEL(nvls_allreduce, KernelId::NVLS_TWOSHOT)
 FR_DEFINE_KERNEL(nvls_oneshot_allreduce, KernelId::NVLS_ONESHOT)
 FR_DEFINE_KERNEL(direct_allreduce, KernelId::P2P_DIRECT)
 FR_DEFINE_KERNEL(nvls_direct_allreduce, KernelId::NVLS_DIRECT)
+FR_DEFINE_KERNEL(ll_allreduce, KernelId::LL_ONESHOT)
 
 
 using KernelFn = void (*)(const ChannelDev*, const OpArgs);
@@ -891,6 +1034,9 @@ KernelFn kernelFor(KernelId id) {
       if constexpr (std::is_same<IO, WIRE>::value &&
                     std::is_floating_point<typename Tr<WIRE>::Acc>::value && sizeof(WIRE) <= 4)
         return nvls_direct_allreduce<IO, WIRE>;
+      return nullptr;
+    case KernelId::LL_ONESHOT:
+      if constexpr (std::is_same<IO, WIRE>::value) return ll_allreduce<IO, WIRE>;
       return nullptr;
     default: return nullptr;
   }

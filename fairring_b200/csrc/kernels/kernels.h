@@ -23,6 +23,8 @@ struct ChannelDev {
   char* staging[kMaxRanks];     // rank p's slot as mapped in this process
   uint32_t* flags[kMaxRanks];   // rank p's flag pad: [source rank][block]
   char* mc_staging;             // NVLS multicast alias of the slot, or null
+  char* ll[kMaxRanks];          // rank p's flag-in-data area (two halves), or null
+  uint64_t ll_half_bytes;       // bytes of one half of that area
   uint32_t* seq;                // local, [kMaxBlocks]: collectives done by block b
   uint32_t* status;             // host-mapped, kStatusWords words, 0 == healthy
   const uint32_t* abort_flag;   // host-mapped; non-zero makes every wait give up
@@ -55,6 +57,7 @@ struct OpArgs {
   int32_t io_dtype;    // DType of in/out
   int32_t wire_dtype;  // DType held in staging and sent over NVLink
   uint32_t flags;      // OpFlags
+  int32_t unroll;      // in-place NVLS kernel: 16-byte accesses in flight per thread (4, 8, 16)
 };
 
 enum class KernelId : int32_t {
@@ -68,6 +71,8 @@ enum class KernelId : int32_t {
   NVLS_ONESHOT,         // multimem.ld_reduce the whole message
   P2P_DIRECT,           // in place on symmetric memory: pull + reduce own chunk, push it to all
   NVLS_DIRECT,          // in place on symmetric memory: multimem.ld_reduce + multimem.st
+  LL_ONESHOT,           // small messages: every 16-byte store carries 8 bytes of data and two
+                        // copies of the collective's number; receivers spin on the data itself
   PIPE,                 // ordinary tensors: copy-in / reduce / copy-out pipelined over chunks
                         // (pipe_allreduce.h; counted here, launched through launchPipeAllreduce)
   kCount

@@ -18,7 +18,8 @@ using namespace dev;
 
 constexpr int kMaxStages = 8;
 constexpr int kNR = kPipeRedGroups;
-constexpr int kRedWarps = (kPipeThreads / 32 - 2) / kNR;  // warps per reduce group
+constexpr int kFirstRedWarp = 4;  // warps 0..3: copy-in, copy-out, publisher, spare
+constexpr int kRedWarps = (kPipeThreads / 32 - kFirstRedWarp) / kNR;  // warps per reduce group
 constexpr int kRedThreads = kRedWarps * 32;
 
 enum Where : uint32_t {  // second status word: which wait gave up
@@ -26,50 +27,56 @@ enum Where : uint32_t {  // second status word: which wait gave up
   kWaitReduce = 101,     // copy-out waiting for a peer's reduce counter
   kWaitSlot = 102,       // copy-in waiting for this block's copy-out (ring slot reuse)
   kWaitBulk = 103,       // a bulk copy into shared memory did not complete
+  kWaitCopyInLocal = 104,  // the publisher waiting for this block's own copy-in
 };
 
 struct Ctl {  // block-shared control words
   unsigned long long full[2][kMaxStages];  // mbarriers: data of stage s has landed ([role][stage])
   volatile uint32_t cout_done;             // chunks (numbered across launches) copied out by this block
+  volatile uint32_t cin_done;              // chunks whose copy-in stores are complete (not yet published)
   volatile uint32_t failed;                // some wait of this block gave up
 };
 
 struct Geo {
   int64_t nvec;  // 16-byte vectors in the message (the last one may be partial)
   int64_t cv;    // vectors per chunk
+  int64_t sv;    // vectors per sub-chunk (what one rank reduces of a full chunk)
+  int64_t pv;    // vectors per piece (one block's part of a sub-chunk)
   int32_t nchunks;
   int32_t tail;  // bytes in the partial last vector, 0 if the message is whole vectors
-  int32_t W, G, b, pad_;
+  int32_t W, G, b, slots;
 };
 
 struct Piece {
   int64_t lo, hi;  // message vectors [lo, hi)
 };
 
-// Block b's part of sub-chunk j of chunk k.  Sub-chunk j is what rank j reduces.
-// The cut is the same for every chunk of a launch (it is made on the full
-// chunk length and clipped to the message), so a position of a ring slot is
-// always owned by the same block: a block that waits for its own copy-out of
-// the slot's previous chunk has waited for all readers of what it overwrites.
-__device__ __forceinline__ Piece pieceOf(const Geo& g, int k, int j, int b) {
-  const int64_t c_lo = (int64_t)k * g.cv;
+// Block b's part of sub-chunk j of the chunk that starts at vector c_lo.
+// Sub-chunk j is what rank j reduces.  The cut is the same for every chunk of a
+// launch (it is made on the full chunk length and clipped to the message), so a
+// position of a ring slot is always owned by the same block: a block that waits
+// for its own copy-out of the slot's previous chunk has waited for all readers
+// of what it overwrites.  (No division here: the copy warps run this per piece.)
+__device__ __forceinline__ Piece pieceAt(const Geo& g, int64_t c_lo, int j, int b) {
   const int64_t c_hi = c_lo + g.cv < g.nvec ? c_lo + g.cv : g.nvec;
-  const int64_t sv = ceilDiv(g.cv, g.W);
-  const int64_t s_lo = c_lo + (int64_t)j * sv;
-  const int64_t s_hi = s_lo + sv < c_hi ? s_lo + sv : c_hi;
-  const int64_t pv = ceilDiv(sv, g.G);
+  const int64_t s_lo = c_lo + (int64_t)j * g.sv;
+  const int64_t s_hi = s_lo + g.sv < c_hi ? s_lo + g.sv : c_hi;
   Piece p;
-  p.lo = s_lo + (int64_t)b * pv;
-  p.hi = p.lo + pv < s_hi ? p.lo + pv : s_hi;
+  p.lo = s_lo + (int64_t)b * g.pv;
+  p.hi = p.lo + g.pv < s_hi ? p.lo + g.pv : s_hi;
   if (p.hi < p.lo) p.hi = p.lo;
   return p;
 }
 
 // Walks the items of this block in order: for every chunk k the non-empty
 // pieces of sub-chunks 0..W-1 (partial tail vector left out), then an
-// end-of-chunk marker (j == W).
+// end-of-chunk marker (j == W).  Keeps the chunk's first vector and ring slot
+// up to date by increments.
 struct Cursor {
   int32_t k, j;
+  int32_t slot;   // ring slot of chunk k
+  int32_t pad_;
+  int64_t c_lo;   // first vector of chunk k
   int64_t lo, hi;
 };
 __device__ __forceinline__ void cursorNext(Cursor& c, const Geo& g, int64_t took) {
@@ -77,31 +84,35 @@ __device__ __forceinline__ void cursorNext(Cursor& c, const Geo& g, int64_t took
     ++c.k;
     c.j = -1;
     c.lo = c.hi = 0;
+    c.c_lo += g.cv;
+    if (++c.slot == g.slots) c.slot = 0;
   } else {
     c.lo += took;
   }
   while (c.k < g.nchunks && c.lo >= c.hi) {
     ++c.j;
     if (c.j == g.W) return;
-    Piece p = pieceOf(g, c.k, c.j, g.b);
+    Piece p = pieceAt(g, c.c_lo, c.j, g.b);
     if (g.tail != 0 && p.hi == g.nvec && p.hi > p.lo) --p.hi;
     c.lo = p.lo;
     c.hi = p.hi;
   }
 }
-__device__ __forceinline__ void cursorInit(Cursor& c, const Geo& g) {
+__device__ __forceinline__ void cursorInit(Cursor& c, const Geo& g, uint32_t g0) {
   c.k = 0;
   c.j = -1;
+  c.slot = (int32_t)(g0 % (uint32_t)g.slots);
+  c.c_lo = 0;
   c.lo = c.hi = 0;
   cursorNext(c, g, 0);
 }
 
 // Does this block own the (partial) last vector of the message, and is that
-// vector in chunk k?
-__device__ __forceinline__ bool ownsTail(const Geo& g, int k) {
+// vector in the chunk (number k) that starts at c_lo?
+__device__ __forceinline__ bool ownsTail(const Geo& g, int k, int64_t c_lo) {
   if (g.tail == 0 || k != g.nchunks - 1) return false;
   for (int j = 0; j < g.W; ++j) {
-    const Piece p = pieceOf(g, k, j, g.b);
+    const Piece p = pieceAt(g, c_lo, j, g.b);
     if (p.hi == g.nvec && p.hi > p.lo) return true;
   }
   return false;
@@ -144,9 +155,6 @@ __device__ __forceinline__ void bulkStore(void* gdst, const void* smem_src, uint
                : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
-__device__ __forceinline__ void bulkWaitRead1() {
-  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-}
 __device__ __forceinline__ void bulkWaitAll() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
@@ -167,7 +175,9 @@ __device__ __forceinline__ bool namedBarrierOr(int id, int count, bool pred) {
 // ---- bounded waits -------------------------------------------------------------
 __device__ __forceinline__ void recordFailure(const PipeChannelDev& c, Ctl* ctl, uint32_t code,
                                               uint32_t where, uint32_t peer, uint32_t chunk) {
-  ctl->failed = 1;
+  // The first failure of a block is the one worth reporting: the waits that
+  // give up after it do so because of it.
+  if (atomicExch(const_cast<uint32_t*>(&ctl->failed), 1u) != 0u) return;
   volatile uint32_t* s = c.status;
   s[1] = where;
   s[2] = peer;
@@ -243,13 +253,38 @@ __device__ __forceinline__ uint32_t* counterAt(uint32_t* pad, int lane_idx, int 
   return pad + ((size_t)lane_idx * kMaxRanks + src) * kMaxBlocks + b;
 }
 
-__device__ __forceinline__ uint64_t slotOffset(const PipeChannelDev& c, uint32_t g) {
-  return (uint64_t)(g % (uint32_t)c.slots) * c.slot_bytes;
+__device__ __forceinline__ uint64_t slotOffset(const PipeChannelDev& c, int slot) {
+  return (uint64_t)slot * c.slot_bytes;
 }
 
 // ---- the two copy roles ------------------------------------------------------
+// wait_group takes an immediate operand.
+__device__ __forceinline__ void bulkWaitReadN(int n) {
+  switch (n) {
+    case 0: asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory"); break;
+    default: asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory"); break;
+  }
+}
+__device__ __forceinline__ void bulkWaitN(int n) {
+  switch (n) {
+    case 0: asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); break;
+    default: asm volatile("cp.async.bulk.wait_group 3;" ::: "memory"); break;
+  }
+}
+
 // CIN: user tensor -> own ring slot.  !CIN: own ring slot -> user tensor.
 // One warp; lane 0 issues the bulk copies and owns their bulk async-groups.
+// Half of the stages are being filled by loads while the other half is being
+// drained by stores.  Copy-in does not stop at the end of a chunk: the chunk's
+// counter is published a few stores later, once wait_group says that its
+// stores are complete.
+// The warp is alone with its instruction stream, so the per-copy path is kept
+// to a pointer, a byte count and two stage indices; the cursor arithmetic runs
+// once per piece.
 template <bool CIN>
 __device__ __forceinline__ void copyRole(const PipeChannelDev& c, const PipeArgs& a, const Geo& g,
                                          Ctl* ctl, unsigned char* stage_base, uint32_t g0,
@@ -257,130 +292,293 @@ __device__ __forceinline__ void copyRole(const PipeChannelDev& c, const PipeArgs
   const int lane = threadIdx.x & 31;
   const int role = CIN ? 0 : 1;
   const uint32_t NS = (uint32_t)a.stages;
-  const int64_t SV = a.stage_bytes / kVecBytes;
+  const uint32_t stage_bytes = (uint32_t)a.stage_bytes;
+  int keep = (int)NS / 2 - 1;  // stores that may still be reading their stage after a wait
+  if (keep > 3) keep = 3;
+  if (keep < 0) keep = 0;
   char* own = c.ring[c.rank];
   uint32_t* my_pad = c.flags[c.rank];
   Cursor ld, st;
-  cursorInit(ld, g);
-  cursorInit(st, g);
+  cursorInit(ld, g, g0);
+  cursorInit(st, g, g0);
   uint32_t nld = 0, nst = 0, freed = 0;  // loads issued, stores issued, stages released by stores
-  int ld_open = -1;     // copy-out: last chunk whose reduce counters were seen complete
-  int st_started = -1;  // copy-in: last chunk whose ring slot was seen free
+  uint32_t ls = 0, ss = 0, sph = 0;      // stage of the next load, of the next store, its phase
+  const char* l_src = nullptr;           // rest of the piece being loaded
+  uint32_t l_left = 0;
+  char* s_dst = nullptr;                 // rest of the piece being stored
+  uint32_t s_left = 0;
+  int ld_open = -1;      // copy-out: last chunk whose reduce counters were seen complete
+  int st_started = -1;   // copy-in: last chunk whose ring slot was seen free
+  int pend_k = -1;       // copy-in: chunk whose counter is not yet published
+  uint32_t pend_at = 0;  // ... and the number of stores issued when it ended
   bool ok = true;
 
-  while (ok && st.k < g.nchunks) {
-    // Issue loads ahead of the stores while shared-memory stages are free.
-    while (ld.k < g.nchunks && nld < freed + NS) {
-      if (ld.j == g.W) {
-        cursorNext(ld, g, 0);
-        continue;
-      }
-      if (!CIN && ld.k > ld_open) {
-        // The reduced chunk must have landed in this GPU's slot: every rank's
-        // reduce counter for it.  Only block when nothing is loaded ahead.
-        const uint32_t gg = g0 + (uint32_t)ld.k;
-        const uint32_t* f = counterAt(my_pad, 1 + (int)(gg % kNR), lane < g.W ? lane : 0, g.b);
-        bool ready;
-        if (nld == nst) {
-          bool mine = true;
-          if (lane < g.W) mine = waitCounter(c, ctl, f, gg + 1u, kWaitReduce, (uint32_t)lane);
-          ready = __all_sync(0xffffffffu, mine);
-          if (!ready) {
-            ok = false;
-            break;
-          }
-        } else {
-          const bool mine = lane >= g.W || (int32_t)(ldAcquireSys(f) - (gg + 1u)) >= 0;
-          ready = __all_sync(0xffffffffu, mine);
-          if (!ready) break;
-        }
-        ld_open = ld.k;
-        fenceProxyAsync();  // peers' generic-proxy writes before this thread's bulk reads
-      }
-      const int64_t take = ld.hi - ld.lo < SV ? ld.hi - ld.lo : SV;
-      if (lane == 0) {
-        const uint32_t s = nld % NS;
-        const char* src = CIN ? user_in + ld.lo * kVecBytes
-                              : own + slotOffset(c, g0 + (uint32_t)ld.k) +
-                                    (ld.lo - (int64_t)ld.k * g.cv) * kVecBytes;
-        mbarExpectTx(&ctl->full[role][s], (uint32_t)(take * kVecBytes));
-        bulkLoad(stage_base + (size_t)s * a.stage_bytes, src, (uint32_t)(take * kVecBytes),
-                 &ctl->full[role][s]);
-      }
-      ++nld;
-      cursorNext(ld, g, take);
+  if (!CIN && (a.debug & 4)) {  // TEMP probe: copy-out only follows the counters
+    for (int k = 0; k < g.nchunks; ++k) {
+      const uint32_t gg = g0 + (uint32_t)k;
+      bool mine = true;
+      if (lane < g.W) mine = waitCounter(c, ctl, counterAt(my_pad, 1 + (int)(gg % kNR), lane, g.b), gg + 1u, kWaitReduce, lane);
+      if (!__all_sync(0xffffffffu, mine)) return;
+      if (lane == 0) ctl->cout_done = gg + 1u;
     }
-    if (!ok) break;
+    return;
+  }
 
-    const uint32_t gg = g0 + (uint32_t)st.k;
-    if (CIN && st.k > st_started) {
-      if (!__all_sync(0xffffffffu, waitSlotFree(c, ctl, gg))) {
-        ok = false;
-        break;
-      }
-      st_started = st.k;
+  // Copy-in: chunk k of this block is in the ring (its bulk stores are complete
+  // and so are the tail bytes).  The publisher warp tells the peers.
+  auto publish = [&](int k) {
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      ctl->cin_done = g0 + (uint32_t)k + 1u;
     }
-    if (st.j == g.W) {
-      // End of chunk st.k.
-      const bool tail_here = ownsTail(g, st.k);
-      const int64_t tv = g.nvec - 1;  // the partial vector
-      char* ring_tail = own + slotOffset(c, gg) + (tv - (int64_t)st.k * g.cv) * kVecBytes;
-      if (CIN) {
-        if (tail_here && lane < kVecBytes) {
+  };
+  auto waitReduced = [&](int k, bool block) -> int {  // copy-out: 1 ready, 0 not yet, -1 failed
+    const uint32_t gg = g0 + (uint32_t)k;
+    const uint32_t* f = counterAt(my_pad, 1 + (int)(gg % kNR), lane < g.W ? lane : 0, g.b);
+    bool mine = true;
+    if (block) {
+      if (lane < g.W) mine = waitCounter(c, ctl, f, gg + 1u, kWaitReduce, (uint32_t)lane);
+      if (!__all_sync(0xffffffffu, mine)) return -1;
+    } else {
+      mine = lane >= g.W || (int32_t)(ldAcquireSys(f) - (gg + 1u)) >= 0;
+      if (!__all_sync(0xffffffffu, mine)) return 0;
+    }
+    fenceProxyAsync();  // peers' generic-proxy writes before this thread's bulk reads
+    return 1;
+  };
+  // Moves the load side to its next piece.  1: l_src/l_left are set; 0: nothing
+  // to load right now (message done, or the next chunk is not reduced yet);
+  // -1: a wait failed.
+  auto nextLoadPiece = [&]() -> int {
+    while (ld.k < g.nchunks && ld.j == g.W) cursorNext(ld, g, 0);
+    if (ld.k >= g.nchunks) return 0;
+    if (!CIN && ld.k > ld_open) {
+      // Only block when nothing is loaded ahead of the stores.
+      const int r = waitReduced(ld.k, nld == nst);
+      if (r <= 0) return r;
+      ld_open = ld.k;
+    }
+    l_src = CIN ? user_in + ld.lo * kVecBytes
+                : own + slotOffset(c, ld.slot) + (ld.lo - ld.c_lo) * kVecBytes;
+    l_left = (uint32_t)((ld.hi - ld.lo) * kVecBytes);
+    cursorNext(ld, g, ld.hi - ld.lo);
+    return 1;
+  };
+  // End of chunk st.k on the store side.
+  auto endOfChunk = [&]() -> bool {
+    const uint32_t gg = g0 + (uint32_t)st.k;
+    const bool tail_here = ownsTail(g, st.k, st.c_lo);
+    const int64_t tv = g.nvec - 1;  // the partial vector
+    char* ring_tail = own + slotOffset(c, st.slot) + (tv - st.c_lo) * kVecBytes;
+    if (CIN) {
+      if (tail_here) {
+        if (st.k > st_started) {
+          if (!__all_sync(0xffffffffu, waitSlotFree(c, ctl, gg))) return false;
+          st_started = st.k;
+        }
+        if (lane < kVecBytes) {
           const unsigned char v = lane < g.tail ? (unsigned char)user_in[tv * kVecBytes + lane] : 0;
           *reinterpret_cast<volatile unsigned char*>(ring_tail + lane) = v;
         }
-        if (lane == 0) {
-          bulkWaitAll();  // this chunk's bulk stores have been written
-          __threadfence_system();
-        }
-        freed = nst;  // ... so every stage is free again
-        __syncwarp();
-        if (lane < g.W) {
-          __threadfence_system();
-          stReleaseSys(counterAt(c.flags[lane], 0, c.rank, g.b), gg + 1u);
-        }
+      }
+      if (pend_k >= 0 || st.k == g.nchunks - 1) {
+        // An earlier chunk is still unpublished, or nothing follows: drain.
+        if (lane == 0) bulkWaitAll();
+        freed = nst;
+        if (pend_k >= 0) publish(pend_k);
+        publish(st.k);
+        pend_k = -1;
       } else {
-        if (tail_here && lane < g.tail)
-          user_out[tv * kVecBytes + lane] =
-              *reinterpret_cast<volatile unsigned char*>(ring_tail + lane);
-        __syncwarp();
-        if (lane == 0) {
-          __threadfence_block();
-          ctl->cout_done = gg + 1u;  // every bulk load of the chunk was waited for above
-        }
+        pend_k = st.k;
+        pend_at = nst;
       }
-      cursorNext(st, g, 0);
-      continue;
-    }
-    // A piece: its load was issued above (nld > nst here).
-    {
-      const uint32_t s = nst % NS;
-      if (!__all_sync(0xffffffffu, mbarWait(c, ctl, &ctl->full[role][s], (nst / NS) & 1u, gg))) {
-        ok = false;
-        break;
+    } else {
+      if (tail_here && st.k > ld_open) {
+        // No whole vector of this chunk came through the loads, so its reduce
+        // counters have not been waited for yet.
+        if (waitReduced(st.k, true) < 0) return false;
+        ld_open = st.k;
       }
-      const int64_t take = st.hi - st.lo < SV ? st.hi - st.lo : SV;
-      if (lane == 0) {
-        char* dst = CIN ? own + slotOffset(c, gg) + (st.lo - (int64_t)st.k * g.cv) * kVecBytes
-                        : user_out + st.lo * kVecBytes;
-        bulkStore(dst, stage_base + (size_t)s * a.stage_bytes, (uint32_t)(take * kVecBytes));
-        bulkWaitRead1();  // every store but this one has finished reading its stage
-      }
-      ++nst;
-      freed = nst - 1;
-      cursorNext(st, g, take);
+      if (tail_here && lane < g.tail)
+        user_out[tv * kVecBytes + lane] = *reinterpret_cast<volatile unsigned char*>(ring_tail + lane);
       __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();
+        ctl->cout_done = gg + 1u;  // every bulk load of the chunk has been waited for
+      }
     }
+    return true;
+  };
+
+  for (;;) {
+    // Store side: find the next piece, closing chunks on the way.
+    if (s_left == 0) {
+      while (st.k < g.nchunks && st.j == g.W) {
+        if (!endOfChunk()) {
+          ok = false;
+          break;
+        }
+        cursorNext(st, g, 0);
+      }
+      if (!ok || st.k >= g.nchunks) break;
+      if (CIN && st.k > st_started) {
+        if (!__all_sync(0xffffffffu, waitSlotFree(c, ctl, g0 + (uint32_t)st.k))) {
+          ok = false;
+          break;
+        }
+        st_started = st.k;
+      }
+      s_dst = CIN ? own + slotOffset(c, st.slot) + (st.lo - st.c_lo) * kVecBytes
+                  : user_out + st.lo * kVecBytes;
+      s_left = (uint32_t)((st.hi - st.lo) * kVecBytes);
+      cursorNext(st, g, st.hi - st.lo);
+    }
+    // Loads run ahead of the stores while shared-memory stages are free.
+    while (nld < freed + NS) {
+      if (l_left == 0) {
+        const int r = nextLoadPiece();
+        if (r < 0) ok = false;
+        if (r <= 0) break;
+      }
+      const uint32_t take = l_left < stage_bytes ? l_left : stage_bytes;
+      if (lane == 0) {
+        mbarExpectTx(&ctl->full[role][ls], take);
+        bulkLoad(stage_base + (size_t)ls * stage_bytes, l_src, take, &ctl->full[role][ls]);
+      }
+      l_src += take;
+      l_left -= take;
+      ++nld;
+      if (++ls == NS) ls = 0;
+    }
+    if (!ok) break;
+    // The next copy of the store side: its load was issued above (nld > nst).
+    if (!__all_sync(0xffffffffu, mbarWait(c, ctl, &ctl->full[role][ss], sph, g0 + (uint32_t)st.k))) {
+      ok = false;
+      break;
+    }
+    const uint32_t take = s_left < stage_bytes ? s_left : stage_bytes;
+    ++nst;
+    const bool settle = CIN && pend_k >= 0 && nst - pend_at >= (uint32_t)keep;
+    if (lane == 0) {
+      bulkStore(s_dst, stage_base + (size_t)ss * stage_bytes, take);
+      // All but the newest `keep` stores have finished reading their stage --
+      // or, when a chunk waits to be published, have been written altogether.
+      if (settle)
+        bulkWaitN(keep);
+      else
+        bulkWaitReadN(keep);
+    }
+    s_dst += take;
+    s_left -= take;
+    if (++ss == NS) {
+      ss = 0;
+      sph ^= 1u;
+    }
+    freed = nst > (uint32_t)keep ? nst - (uint32_t)keep : 0;
+    if (settle) {
+      publish(pend_k);
+      pend_k = -1;
+    }
+    __syncwarp();
   }
   // Leave nothing in flight: stores first, then loads that were never consumed.
   if (lane == 0) bulkWaitAll();
-  for (uint32_t i = nst; i < nld; ++i)
-    mbarWait(c, ctl, &ctl->full[role][i % NS], (i / NS) & 1u, 0, /*heed_failed=*/false);
+  if (CIN && ok && pend_k >= 0) publish(pend_k);
+  for (uint32_t i = nst; i < nld; ++i) {
+    mbarWait(c, ctl, &ctl->full[role][ss], sph, 0, /*heed_failed=*/false);
+    if (++ss == NS) {
+      ss = 0;
+      sph ^= 1u;
+    }
+  }
   __syncwarp();
 }
 
+// ---- the publisher ------------------------------------------------------------
+// Waits for copy-in's word in shared memory, then makes the chunk visible to the
+// other GPUs (fence) and raises this block's copy-in counter on every rank.
+__device__ __forceinline__ void publishRole(const PipeChannelDev& c, const PipeArgs& a, const Geo& g,
+                                            Ctl* ctl, uint32_t g0) {
+  const int lane = threadIdx.x & 31;
+  for (int k = 0; k < g.nchunks; ++k) {
+    const uint32_t want = g0 + (uint32_t)k + 1u;
+    bool mine = true;
+    if (lane == 0) {
+      uint64_t t0 = 0;
+      for (uint64_t n = 1;; ++n) {
+        if ((int32_t)(ctl->cin_done - want) >= 0) break;
+        if ((n & 255) == 0) {
+          if (ctl->failed) {
+            mine = false;
+            break;
+          }
+          const uint64_t now = globalTimerNs();
+          if (t0 == 0) t0 = now;
+          if (now - t0 > c.timeout_ns || n > (1ull << 34)) {
+            recordFailure(c, ctl, kStatusTimeout, kWaitCopyInLocal, (uint32_t)c.rank, want - 1u);
+            mine = false;
+            break;
+          }
+        }
+      }
+    }
+    if (!__all_sync(0xffffffffu, mine)) return;
+    if (lane < g.W) {
+      if (!(a.debug & 2)) __threadfence_system();
+      stReleaseSys(counterAt(c.flags[lane], 0, c.rank, g.b), want);
+    }
+  }
+}
+
 // ---- the reduce role ----------------------------------------------------------
+// Peer-load flavour: read the vector from every rank's ring, reduce in rank
+// order (the same bits on every GPU), write the result into every rank's ring.
+// U vectors per thread and step, at most KW ranks.
+template <typename T, int U, int KW>
+__device__ __forceinline__ void reducePeers(const PipeChannelDev& c, const PipeArgs& a, uint64_t base,
+                                            int64_t n, int gtid) {
+  constexpr int V = kVecBytes / sizeof(T);
+  using Acc = typename Tr<T>::Acc;
+  const int W = c.world;
+  for (int64_t i0 = gtid; i0 < n; i0 += (int64_t)kRedThreads * U) {
+    uint4 raw[U][KW];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + (int64_t)u * kRedThreads;
+#pragma unroll
+      for (int q = 0; q < KW; ++q)
+        if (q < W && i < n) raw[u][q] = ldStage(c.ring[q] + base + i * kVecBytes);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + (int64_t)u * kRedThreads;
+      if (i >= n) continue;
+      Acc acc[V];
+      unpack<T, V>(raw[u][0], acc);
+#pragma unroll
+      for (int q = 1; q < KW; ++q) {
+        if (q < W) {
+          Acc x[V];
+          unpack<T, V>(raw[u][q], x);
+#pragma unroll
+          for (int e = 0; e < V; ++e) acc[e] = combine(acc[e], x[e], a.op);
+        }
+      }
+      if constexpr (std::is_floating_point<Acc>::value) {
+        if (a.scale != 1.0f) {
+#pragma unroll
+          for (int e = 0; e < V; ++e) acc[e] = acc[e] * (Acc)a.scale;
+        }
+      }
+      const uint4 r = pack<T, V>(acc);
+#pragma unroll
+      for (int q = 0; q < KW; ++q)
+        if (q < W) stStage(c.ring[(c.rank + q) % W] + base + i * kVecBytes, r);
+    }
+  }
+}
+
 template <typename T, bool NVLS>
 __device__ __forceinline__ void reducePiece(const PipeChannelDev& c, const PipeArgs& a,
                                             uint64_t slot_off, int64_t first_vec, int64_t n,
@@ -415,44 +613,13 @@ __device__ __forceinline__ void reducePiece(const PipeChannelDev& c, const PipeA
       }
     }
   } else {
-    constexpr int U = 2;
-    const int W = c.world;
-    for (int64_t i0 = gtid; i0 < n; i0 += (int64_t)kRedThreads * U) {
-      uint4 raw[U][kMaxRanks];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int64_t i = i0 + (int64_t)u * kRedThreads;
-#pragma unroll
-        for (int q = 0; q < kMaxRanks; ++q)
-          if (q < W && i < n) raw[u][q] = ldStage(c.ring[q] + base + i * kVecBytes);
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int64_t i = i0 + (int64_t)u * kRedThreads;
-        if (i >= n) continue;
-        Acc acc[V];
-        unpack<T, V>(raw[u][0], acc);  // rank order: the same bits on every GPU
-#pragma unroll
-        for (int q = 1; q < kMaxRanks; ++q) {
-          if (q < W) {
-            Acc x[V];
-            unpack<T, V>(raw[u][q], x);
-#pragma unroll
-            for (int e = 0; e < V; ++e) acc[e] = combine(acc[e], x[e], a.op);
-          }
-        }
-        if constexpr (std::is_floating_point<Acc>::value) {
-          if (a.scale != 1.0f) {
-#pragma unroll
-            for (int e = 0; e < V; ++e) acc[e] = acc[e] * (Acc)a.scale;
-          }
-        }
-        const uint4 r = pack<T, V>(acc);
-#pragma unroll
-        for (int q = 0; q < kMaxRanks; ++q)
-          if (q < W) stStage(c.ring[(c.rank + q) % W] + base + i * kVecBytes, r);
-      }
-    }
+    // Eight 16-byte peer loads in flight per thread whatever the number of ranks.
+    if (c.world <= 2)
+      reducePeers<T, 4, 2>(c, a, base, n, gtid);
+    else if (c.world <= 4)
+      reducePeers<T, 2, 4>(c, a, base, n, gtid);
+    else
+      reducePeers<T, 1, kMaxRanks>(c, a, base, n, gtid);
   }
 }
 
@@ -461,19 +628,22 @@ __device__ __forceinline__ void reduceRole(const PipeChannelDev& c, const PipeAr
                                            Ctl* ctl, uint32_t g0, int group, int gtid) {
   const int bar_id = 1 + group;
   uint32_t* my_pad = c.flags[c.rank];
-  for (int k = 0; k < g.nchunks; ++k) {
+  // This group's first chunk, then every kNR-th one.
+  int k = (int)((uint32_t)(group + kNR) - g0 % kNR) % kNR;
+  int slot = (int)((g0 + (uint32_t)k) % (uint32_t)g.slots);
+  for (; k < g.nchunks; k += kNR, slot = (slot + kNR) % g.slots) {
     const uint32_t gg = g0 + (uint32_t)k;
-    if ((int)(gg % kNR) != group) continue;
     bool bad = false;
     if (gtid < g.W)
       bad = !waitCounter(c, ctl, counterAt(my_pad, 0, gtid, g.b), gg + 1u, kWaitCopyIn, (uint32_t)gtid);
     if (namedBarrierOr(bar_id, kRedThreads, bad || ctl->failed != 0)) break;
-    const Piece p = pieceOf(g, k, c.rank, g.b);  // whole vectors, the padded tail vector included
-    if (p.hi > p.lo)
-      reducePiece<T, NVLS>(c, a, slotOffset(c, gg), p.lo - (int64_t)k * g.cv, p.hi - p.lo, gtid);
+    const int64_t c_lo = (int64_t)k * g.cv;
+    const Piece p = pieceAt(g, c_lo, c.rank, g.b);  // whole vectors, the padded tail vector included
+    if (p.hi > p.lo && !(a.debug & 1))
+      reducePiece<T, NVLS>(c, a, slotOffset(c, slot), p.lo - c_lo, p.hi - p.lo, gtid);
     if (namedBarrierOr(bar_id, kRedThreads, ctl->failed != 0)) break;
     if (gtid < g.W) {
-      __threadfence_system();
+      if (!(a.debug & 2)) __threadfence_system();
       stReleaseSys(counterAt(c.flags[gtid], 1 + group, c.rank, g.b), gg + 1u);
     }
   }
@@ -496,12 +666,16 @@ pipe_allreduce(const PipeChannelDev* __restrict__ chs, const __grid_constant__ P
   g.W = c.world;
   g.G = gridDim.x;
   g.b = blockIdx.x;
+  g.slots = c.slots;
+  g.sv = ceilDiv(g.cv, g.W);
+  g.pv = ceilDiv(g.sv, g.G);
   const uint32_t g0 = c.seq[g.b];
 
   if (threadIdx.x == 0) {
     for (int r = 0; r < 2; ++r)
       for (int s = 0; s < a.stages; ++s) mbarInit(&ctl->full[r][s], 1);
     ctl->cout_done = g0;
+    ctl->cin_done = g0;
     ctl->failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -513,9 +687,11 @@ pipe_allreduce(const PipeChannelDev* __restrict__ chs, const __grid_constant__ P
   } else if (warp == 1) {
     copyRole<false>(c, a, g, ctl, stages + (size_t)a.stages * a.stage_bytes, g0, nullptr,
                     static_cast<char*>(a.out[blockIdx.y]));
-  } else {
-    const int group = (warp - 2) / kRedWarps;
-    const int gtid = (int)threadIdx.x - (2 + group * kRedWarps) * 32;
+  } else if (warp == 2) {
+    publishRole(c, a, g, ctl, g0);
+  } else if (warp >= kFirstRedWarp) {
+    const int group = (warp - kFirstRedWarp) / kRedWarps;
+    const int gtid = (int)threadIdx.x - (kFirstRedWarp + group * kRedWarps) * 32;
     reduceRole<T, NVLS>(c, a, g, ctl, g0, group, gtid);
   }
   __syncthreads();

@@ -7,7 +7,12 @@
 //   copy-in   one warp; bulk-copies (cp.async.bulk through shared memory, one
 //             elected thread) this block's pieces of chunk k from the user's
 //             tensor into this GPU's slot of a ring of symmetric staging memory
-//   reduce    the other warps, in two alternating groups; rank r reduces
+//   publish   one warp; once copy-in says that a chunk's bulk stores are
+//             complete it fences and tells the peers -- the fence takes
+//             microseconds and must not stall the copy-in warp
+//   reduce    twelve warps in six groups that take chunks in turn, so that the
+//             latency of one chunk's switch round trip and of its fence is
+//             hidden behind five other chunks; rank r reduces
 //             sub-chunk r of the chunk over all GPUs and writes the result back
 //             into every GPU's ring slot (multimem.ld_reduce + multimem.st
 //             through the NVSwitch, or peer loads + peer stores)
@@ -36,10 +41,10 @@
 
 namespace fairring {
 
-constexpr int kPipeRedGroups = 2;                  // reduce groups working on alternate chunks
-constexpr int kPipeLanes = 1 + kPipeRedGroups;     // counter lanes: copy-in, reduce group 0, 1
+constexpr int kPipeRedGroups = 6;                  // reduce groups (2 warps each) taking chunks in turn
+constexpr int kPipeLanes = 1 + kPipeRedGroups;     // counter lanes: copy-in, one per reduce group
 constexpr size_t kPipeFlagBytes = (size_t)kPipeLanes * kMaxRanks * kMaxBlocks * sizeof(uint32_t);
-constexpr int kPipeThreads = 512;                  // 1 copy-in warp, 1 copy-out warp, 2 x 7 reduce warps
+constexpr int kPipeThreads = 512;                  // copy-in, copy-out, publisher, (spare), 6 x 2 reduce warps
 
 // One channel as seen by one rank; lives in device memory.
 struct PipeChannelDev {
@@ -69,6 +74,7 @@ struct PipeArgs {
   int32_t nvls;         // 1: reduce through the multicast address
   int32_t stage_bytes;  // bytes of one shared-memory stage (multiple of 16)
   int32_t stages;       // stages per copy role
+  int32_t debug;        // TEMP probe bits
 };
 
 // Shared memory the kernel needs for (stage_bytes, stages).

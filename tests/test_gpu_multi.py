@@ -289,3 +289,34 @@ def test_absent_rank_times_out_and_engine_recovers():
     assert "rank 1" in outcome
     assert elapsed < 20
     assert res[0][2] == 3.0 and res[1][2] == 3.0
+
+
+# --- the reference-sequence comparison arm (NCCL calls in the reference's order) ---------
+def _refseq(rank, world, gpm):
+    import torch.distributed as dist
+
+    from fairring_b200.bench.refseq import ReferenceSequence
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    rs = ReferenceSequence(world, rank, gpm, dev)
+    out = []
+    for n in (8, 1000, 1 << 20, (1 << 20) + 3):
+        x = torch.full((n,), float(rank + 1), device=dev)
+        for _ in range(3):  # back to back: stages of consecutive calls overlap
+            rs.all_reduce(x)
+        torch.cuda.synchronize()
+        out.append((float(x[0]), float(x[-1])))
+    dist.destroy_process_group()
+    return out
+
+
+@pytest.mark.parametrize("gpm", [1, 2])
+def test_reference_sequence_arm(gpm):
+    if _ngpu() < 2:
+        pytest.skip("needs at least two GPUs")
+    res = run_ranks(_refseq, 2, env={}, args=(gpm,), timeout=180)
+    expect = 3.0 * 2 * 2  # (1 + 2), then doubled twice
+    for first, last in res[0]:
+        assert first == expect and last == expect, res[0]
