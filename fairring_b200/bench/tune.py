@@ -51,6 +51,7 @@ def main(argv=None) -> int:
     os.environ.setdefault("FAIRRING_SM_BUDGET", "148")
     os.environ.setdefault("FAIRRING_PARALLELISM", "4")
     os.environ.setdefault("FAIRRING_LL_MAX", str(256 << 10))
+    os.environ.setdefault("FAIRRING_PIPE_SLOTS", "8")
     os.environ["FAIRRING_TUNING_TABLE"] = "off"
     import fairring_b200
 
@@ -101,6 +102,8 @@ def main(argv=None) -> int:
 
     def add(part, cfg, size, us, bw):
         rows.append({"part": part, **cfg, "bytes": size, "us": round(us, 2), "busbw": round(bw, 1)})
+        if rank == 0:
+            print(json.dumps(rows[-1]), flush=True)
 
     big = [int(x) for x in args.big_sizes.split(",")]
 
@@ -141,7 +144,7 @@ def main(argv=None) -> int:
 
     if "pipe" in what and world > 1:
         setopt(algo=ALGO["pipe"], ll_max_bytes=0)
-        for blocks, chunk in itertools.product((8, 16, 24, 32), (512 << 10, 1 << 20, 2 << 20, 4 << 20)):
+        for blocks, chunk in itertools.product((8, 16, 24, 32), (1 << 20, 2 << 20, 4 << 20, 8 << 20)):
             setopt(pipe_blocks=blocks, pipe_chunk_bytes=chunk)
             for size in [int(x) for x in args.pipe_sizes.split(",")]:
                 us, bw = measure(arena, size)
@@ -154,8 +157,14 @@ def main(argv=None) -> int:
                 us, bw = measure(arena, size)
                 add("pipe", {"blocks": 16, "chunk": 2 << 20, "stage": stage, "stages": stages}, size, us, bw)
         setopt(pipe_stage_bytes=16, pipe_stages=2)
-        setopt(pipe_stages=6, pipe_stage_bytes=16 << 10, pipe_blocks=16, pipe_chunk_bytes=0, algo=ALGO["auto"],
-               ll_max_bytes=32 << 10)
+        setopt(pipe_stages=6, pipe_stage_bytes=16 << 10, pipe_blocks=16, pipe_chunk_bytes=0)
+        # the staged kernels on the same messages (sliced over the channels)
+        for name in ("nvls", "twoshot"):
+            setopt(algo=ALGO[name])
+            for size in [int(x) for x in args.pipe_sizes.split(",")]:
+                us, bw = measure(arena, size)
+                add("staged", {"variant": name}, size, us, bw)
+        setopt(algo=ALGO["auto"], ll_max_bytes=32 << 10)
         be.check_health()
 
     if "small" in what and world > 1:
@@ -178,8 +187,6 @@ def main(argv=None) -> int:
         be.check_health()
 
     if rank == 0:
-        for r in rows:
-            print(json.dumps(r))
         if args.json:
             with open(args.json, "w") as f:
                 json.dump({"describe": be.describe(), "world": world, "dtype": args.dtype, "rows": rows}, f, indent=1)
@@ -191,8 +198,11 @@ def main(argv=None) -> int:
             path.write_text(json.dumps(old, indent=1, sort_keys=True) + "\n")
             print("# wrote", path, json.dumps(table))
     dist.barrier(group=side)
-    dist.destroy_process_group()
-    return 0
+    # Registered NCCL pools and sub-groups do not always come down in order at
+    # interpreter exit; everything has been printed, leave directly.
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def derive_table(rows, world):

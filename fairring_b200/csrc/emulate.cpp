@@ -297,7 +297,6 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedPipeAllreduce(
   a.nvls = 0;
   a.stage_bytes = (int32_t)stage_bytes;
   a.stages = (int32_t)stages;
-  if (const char* dbg = std::getenv("FR_PIPE_DEBUG")) a.debug = std::atoi(dbg);
   cudaEvent_t t0, t1;
   FR_CUDA(cudaEventCreate(&t0));
   FR_CUDA(cudaEventCreate(&t1));

@@ -192,7 +192,10 @@ __device__ __forceinline__ void recordFailure(const PipeChannelDev& c, Ctl* ctl,
 __device__ __forceinline__ bool waitCounter(const PipeChannelDev& c, Ctl* ctl, const uint32_t* flag,
                                             uint32_t want, uint32_t where, uint32_t peer) {
   uint64_t t0 = 0;
-  const uint64_t iter_cap = c.timeout_ns / 32 + (1ull << 20);
+  // A wait on this rank's own counter only fails because something upstream of
+  // it did: give the waits on peers the time to report first.
+  const uint64_t limit = peer == (uint32_t)c.rank ? 2 * c.timeout_ns : c.timeout_ns;
+  const uint64_t iter_cap = limit / 32 + (1ull << 20);
   for (uint64_t n = 1;; ++n) {
     const uint32_t v = ldAcquireSys(flag);
     if ((int32_t)(v - want) >= 0) return true;
@@ -200,7 +203,7 @@ __device__ __forceinline__ bool waitCounter(const PipeChannelDev& c, Ctl* ctl, c
       if (ctl->failed) return false;
       const uint64_t now = globalTimerNs();
       if (t0 == 0) t0 = now;
-      if (now - t0 > c.timeout_ns || n > iter_cap) {
+      if (now - t0 > limit || n > iter_cap) {
         recordFailure(c, ctl, kStatusTimeout, where, peer, want - 1);
         return false;
       }
@@ -222,7 +225,7 @@ __device__ __forceinline__ bool mbarWait(const PipeChannelDev& c, Ctl* ctl, unsi
       if (heed_failed && ctl->failed) return false;
       const uint64_t now = globalTimerNs();
       if (t0 == 0) t0 = now;
-      if (now - t0 > c.timeout_ns || n > (1ull << 34)) {
+      if (now - t0 > 2 * c.timeout_ns || n > (1ull << 34)) {
         recordFailure(c, ctl, kStatusTimeout, kWaitBulk, (uint32_t)c.rank, chunk);
         return false;
       }
@@ -241,7 +244,7 @@ __device__ __forceinline__ bool waitSlotFree(const PipeChannelDev& c, Ctl* ctl, 
       if (ctl->failed) return false;
       const uint64_t now = globalTimerNs();
       if (t0 == 0) t0 = now;
-      if (now - t0 > c.timeout_ns || n > (1ull << 34)) {
+      if (now - t0 > 2 * c.timeout_ns || n > (1ull << 34)) {
         recordFailure(c, ctl, kStatusTimeout, kWaitSlot, (uint32_t)c.rank, g);
         return false;
       }
@@ -312,17 +315,6 @@ __device__ __forceinline__ void copyRole(const PipeChannelDev& c, const PipeArgs
   int pend_k = -1;       // copy-in: chunk whose counter is not yet published
   uint32_t pend_at = 0;  // ... and the number of stores issued when it ended
   bool ok = true;
-
-  if (!CIN && (a.debug & 4)) {  // TEMP probe: copy-out only follows the counters
-    for (int k = 0; k < g.nchunks; ++k) {
-      const uint32_t gg = g0 + (uint32_t)k;
-      bool mine = true;
-      if (lane < g.W) mine = waitCounter(c, ctl, counterAt(my_pad, 1 + (int)(gg % kNR), lane, g.b), gg + 1u, kWaitReduce, lane);
-      if (!__all_sync(0xffffffffu, mine)) return;
-      if (lane == 0) ctl->cout_done = gg + 1u;
-    }
-    return;
-  }
 
   // Copy-in: chunk k of this block is in the ring (its bulk stores are complete
   // and so are the tail bytes).  The publisher warp tells the peers.
@@ -515,7 +507,7 @@ __device__ __forceinline__ void publishRole(const PipeChannelDev& c, const PipeA
           }
           const uint64_t now = globalTimerNs();
           if (t0 == 0) t0 = now;
-          if (now - t0 > c.timeout_ns || n > (1ull << 34)) {
+          if (now - t0 > 2 * c.timeout_ns || n > (1ull << 34)) {
             recordFailure(c, ctl, kStatusTimeout, kWaitCopyInLocal, (uint32_t)c.rank, want - 1u);
             mine = false;
             break;
@@ -525,7 +517,7 @@ __device__ __forceinline__ void publishRole(const PipeChannelDev& c, const PipeA
     }
     if (!__all_sync(0xffffffffu, mine)) return;
     if (lane < g.W) {
-      if (!(a.debug & 2)) __threadfence_system();
+      __threadfence_system();
       stReleaseSys(counterAt(c.flags[lane], 0, c.rank, g.b), want);
     }
   }
@@ -639,11 +631,11 @@ __device__ __forceinline__ void reduceRole(const PipeChannelDev& c, const PipeAr
     if (namedBarrierOr(bar_id, kRedThreads, bad || ctl->failed != 0)) break;
     const int64_t c_lo = (int64_t)k * g.cv;
     const Piece p = pieceAt(g, c_lo, c.rank, g.b);  // whole vectors, the padded tail vector included
-    if (p.hi > p.lo && !(a.debug & 1))
+    if (p.hi > p.lo)
       reducePiece<T, NVLS>(c, a, slotOffset(c, slot), p.lo - c_lo, p.hi - p.lo, gtid);
     if (namedBarrierOr(bar_id, kRedThreads, ctl->failed != 0)) break;
     if (gtid < g.W) {
-      if (!(a.debug & 2)) __threadfence_system();
+      __threadfence_system();
       stReleaseSys(counterAt(c.flags[gtid], 1 + group, c.rank, g.b), gg + 1u);
     }
   }

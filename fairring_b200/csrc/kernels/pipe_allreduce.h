@@ -74,7 +74,6 @@ struct PipeArgs {
   int32_t nvls;         // 1: reduce through the multicast address
   int32_t stage_bytes;  // bytes of one shared-memory stage (multiple of 16)
   int32_t stages;       // stages per copy role
-  int32_t debug;        // TEMP probe bits
 };
 
 // Shared memory the kernel needs for (stage_bytes, stages).
