@@ -22,13 +22,14 @@ import torch
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="twoshot",
-                    choices=["oneshot", "twoshot", "hier", "direct", "adamw", "sumsq"])
+                    choices=["oneshot", "twoshot", "hier", "direct", "ll", "pipe", "adamw", "sumsq"])
     ap.add_argument("--world", type=int, default=8)
     ap.add_argument("--gpus-per-machine", type=int, default=0, help="hier: group size (default world/2)")
     ap.add_argument("--mib", type=float, default=16.0, help="message (or buffer) size per rank, MiB")
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--blocks", type=int, default=16)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--chunk-kib", type=int, default=1024, help="pipe: chunk (and ring slot) size")
     args = ap.parse_args(argv)
 
     from torch.profiler import ProfilerActivity, profile
@@ -54,6 +55,15 @@ def main(argv=None) -> int:
             fn = lambda i: C.sumsq(g)  # noqa: E731
             algo_bytes = n * 4
             pattern = "sumsq"
+    elif args.kernel == "pipe":
+        ins = [torch.randn(n, device="cuda").to(dtype) for _ in range(W)]
+        fn = lambda i: C.emulated_pipe_allreduce(  # noqa: E731
+            ins, blocks=args.blocks, chunk_bytes=args.chunk_kib << 10, slot_bytes=args.chunk_kib << 10,
+            slots=4, stage_bytes=16 << 10, stages=6, scale=1.0 / W)
+        nb = n * es
+        # copy-in (read + write), reduce (W reads, W writes of 1/W each), copy-out (read + write)
+        algo_bytes = (2 * nb + 2 * nb + 2 * nb) * W
+        pattern = "pipe_allreduce"
     else:
         ins = [torch.randn(n, device="cuda").to(dtype) for _ in range(W)]
         gpm = W
@@ -64,12 +74,13 @@ def main(argv=None) -> int:
             "allreduce", ins, gpm, algo=args.kernel, blocks=args.blocks, half_bytes=half)
         nb = n * es
         # HBM bytes the algorithm has to move, summed over the W emulated ranks.
-        per_rank = {"oneshot": nb * (1 + W) + nb * W + nb,      # read in, write W copies; read W, write out
+        per_rank = {"ll": nb * (1 + 2 * W) + 2 * nb * W + nb,  # every 8 bytes travel as 16
+                    "oneshot": nb * (1 + W) + nb * W + nb,      # read in, write W copies; read W, write out
                     "twoshot": 2 * nb + (nb + nb / W) + 2 * nb,  # push; reduce; gather
                     "hier": 2 * nb + (nb + nb / W) + 2 * nb,     # (plus the shard-server pass when M > 1)
                     "direct": nb + nb}[args.kernel]              # read every copy of own chunk, write every copy
         algo_bytes = per_rank * W
-        pattern = {"oneshot": "oneshot_allreduce", "twoshot": "twoshot_allreduce",
+        pattern = {"ll": "ll_allreduce", "oneshot": "oneshot_allreduce", "twoshot": "twoshot_allreduce",
                    "hier": "rs_intragroup|shard_server_reduce|ag_intragroup",
                    "direct": "direct_allreduce"}[args.kernel]
 

@@ -36,22 +36,6 @@ Algo parseAlgo(const std::string& s) {
   return Algo::AUTO;
 }
 
-void CommandQueue::push(std::function<void()> fn) {
-  {
-    std::lock_guard<std::mutex> lk(mu_);
-    q_.push_back(std::move(fn));
-  }
-  cv_.notify_one();
-}
-
-std::function<void()> CommandQueue::pop() {
-  std::unique_lock<std::mutex> lk(mu_);
-  cv_.wait(lk, [&] { return !q_.empty(); });
-  auto fn = std::move(q_.front());
-  q_.pop_front();
-  return fn;
-}
-
 namespace {
 constexpr size_t kFlagPadBytes = (size_t)kMaxRanks * kMaxBlocks * sizeof(uint32_t);
 constexpr size_t kTraceLen = 256;

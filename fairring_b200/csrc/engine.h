@@ -23,6 +23,7 @@
 #include <thread>
 #include <vector>
 
+#include "command_queue.h"
 #include "kernels/kernels.h"
 #include "kernels/pipe_allreduce.h"
 #include "kvstore.h"
@@ -114,19 +115,6 @@ struct TraceEntry {
   int32_t slices = 0;
   int32_t channels = 0;       // side streams used
   double host_us = 0;         // time spent enqueueing
-};
-
-// FIFO of closures drained by one thread (fairring/utils.h:329-351 in the
-// reference).  Used when FAIRRING_COMMAND_THREAD=1.
-class CommandQueue {
- public:
-  void push(std::function<void()> fn);
-  // Blocks; an empty function means "stop".
-  std::function<void()> pop();
- private:
-  std::mutex mu_;
-  std::condition_variable cv_;
-  std::deque<std::function<void()>> q_;
 };
 
 class Engine {

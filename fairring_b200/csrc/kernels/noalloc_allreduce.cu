@@ -22,13 +22,18 @@ constexpr size_t kNaSeqBytes = (size_t)kMaxBlocks * sizeof(uint32_t);
 constexpr int kNaMaxDevices = 64;
 
 // Layout of the static array (offsets are multiples of 256 bytes).
-constexpr size_t kOffChannels = 0;                                              // ChannelDev[8]
-constexpr size_t kOffFlags = 4096;                                              // [8][kNaFlagBytes]
+// One channel table per world size 2..8, all written by the first call on a
+// device, so that later calls only clear the flags and launch.
+constexpr size_t kOffChannels = 0;                                              // [7 tables][ChannelDev[8]]
+constexpr int kNaTables = kNaMaxRanks - 1;
+constexpr size_t kNaTableBytes = 2560;
+constexpr size_t kOffFlags = 20480;                                             // [8][kNaFlagBytes]
 constexpr size_t kOffSeq = kOffFlags + kNaMaxRanks * kNaFlagBytes;              // [8][kNaSeqBytes]
 constexpr size_t kOffStatus = kOffSeq + kNaMaxRanks * kNaSeqBytes;              // [8][4] words + abort word
 constexpr size_t kOffStaging = kOffStatus + 256;                                // [8][kNaHalfBytes]
 constexpr size_t kNaTotal = kOffStaging + kNaMaxRanks * kNaHalfBytes;
-static_assert(sizeof(ChannelDev) * kNaMaxRanks <= 4096, "channel table must fit its slot");
+static_assert(sizeof(ChannelDev) * kNaMaxRanks <= kNaTableBytes, "a channel table must fit its slot");
+static_assert(kNaTables * kNaTableBytes <= kOffFlags, "the tables must fit before the flags");
 static_assert(kOffStaging % 256 == 0, "staging must stay 256-byte aligned");
 
 // The scratch itself.  In host code this name is only a handle for
@@ -37,7 +42,7 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kNaTotal];
 
 struct PerDevice {
   unsigned char* base = nullptr;  // device address of g_noalloc_scratch on that device
-  int world_laid_out = 0;         // the channel table currently describes this many ranks
+  bool laid_out = false;          // the channel tables have been written there
 };
 PerDevice g_dev[kNaMaxDevices];
 std::mutex g_mu;
@@ -67,6 +72,16 @@ extern "C" int fairring_allreduce_f32_noalloc(float* const* bufs, int world, lon
   if (e != cudaSuccess) return fail(2, err, err_len, cudaGetErrorString(e));
   if (dev < 0 || dev >= kNaMaxDevices) return fail(1, err, err_len, "device index out of range");
 
+  for (int r = 0; r < world; ++r) {
+    cudaPointerAttributes attr;
+    e = cudaPointerGetAttributes(&attr, bufs[r]);
+    if (e != cudaSuccess) return fail(2, err, err_len, cudaGetErrorString(e));
+    if (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged)
+      return fail(1, err, err_len, "a buffer is not device memory");
+    if (attr.type == cudaMemoryTypeDevice && attr.device != dev)
+      return fail(1, err, err_len, "a buffer lives on another device than the current one");
+  }
+
   std::lock_guard<std::mutex> lk(g_mu);
   PerDevice& pd = g_dev[dev];
   if (pd.base == nullptr) {
@@ -75,36 +90,39 @@ extern "C" int fairring_allreduce_f32_noalloc(float* const* bufs, int world, lon
     e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess) return fail(2, err, err_len, cudaGetErrorString(e));
     pd.base = static_cast<unsigned char*>(p);
-    pd.world_laid_out = 0;
+    pd.laid_out = false;
   }
   unsigned char* base = pd.base;
 
-  if (pd.world_laid_out != world) {
-    // (Re)write the table that tells each emulated rank where its peers'
-    // staging and flags are.  Pageable-host to device copy: staged by the
-    // driver, nothing is allocated.
-    ChannelDev chs[kNaMaxRanks];
-    std::memset(chs, 0, sizeof(chs));
-    for (int r = 0; r < world; ++r) {
-      ChannelDev& c = chs[r];
-      for (int p = 0; p < world; ++p) {
-        c.staging[p] = reinterpret_cast<char*>(base + kOffStaging + (size_t)p * kNaHalfBytes);
-        c.flags[p] = reinterpret_cast<uint32_t*>(base + kOffFlags + (size_t)p * kNaFlagBytes);
+  if (!pd.laid_out) {
+    // Still the first call: write, for every world size, the table that tells
+    // each emulated rank where its peers' staging and flags are.  Pageable-host
+    // to device copies: staged by the driver, nothing is allocated.  The stream
+    // is synchronised because the tables are built on this stack frame.
+    for (int w = 2; w <= kNaMaxRanks; ++w) {
+      ChannelDev chs[kNaMaxRanks];
+      std::memset(chs, 0, sizeof(chs));
+      for (int r = 0; r < w; ++r) {
+        ChannelDev& c = chs[r];
+        for (int p = 0; p < w; ++p) {
+          c.staging[p] = reinterpret_cast<char*>(base + kOffStaging + (size_t)p * kNaHalfBytes);
+          c.flags[p] = reinterpret_cast<uint32_t*>(base + kOffFlags + (size_t)p * kNaFlagBytes);
+        }
+        c.mc_staging = nullptr;
+        c.seq = reinterpret_cast<uint32_t*>(base + kOffSeq + (size_t)r * kNaSeqBytes);
+        c.status = reinterpret_cast<uint32_t*>(base + kOffStatus) + (size_t)r * kStatusWords;
+        c.abort_flag = reinterpret_cast<uint32_t*>(base + kOffStatus) + kNaMaxRanks * kStatusWords;
+        c.half_bytes = kNaHalfBytes;
+        c.timeout_ns = 2ull * 1000 * 1000 * 1000;
+        c.topo = makeTopo(w, w, false, r);
       }
-      c.mc_staging = nullptr;
-      c.seq = reinterpret_cast<uint32_t*>(base + kOffSeq + (size_t)r * kNaSeqBytes);
-      c.status = reinterpret_cast<uint32_t*>(base + kOffStatus) + (size_t)r * kStatusWords;
-      c.abort_flag = reinterpret_cast<uint32_t*>(base + kOffStatus) + kNaMaxRanks * kStatusWords;
-      c.half_bytes = kNaHalfBytes;
-      c.timeout_ns = 2ull * 1000 * 1000 * 1000;
-      c.topo = makeTopo(world, world, false, r);
+      e = cudaMemcpyAsync(base + kOffChannels + (size_t)(w - 2) * kNaTableBytes, chs,
+                          sizeof(ChannelDev) * w, cudaMemcpyHostToDevice, stream);
+      if (e != cudaSuccess) return fail(2, err, err_len, cudaGetErrorString(e));
+      e = cudaStreamSynchronize(stream);
+      if (e != cudaSuccess) return fail(2, err, err_len, cudaGetErrorString(e));
     }
-    e = cudaMemcpyAsync(base + kOffChannels, chs, sizeof(ChannelDev) * world,
-                        cudaMemcpyHostToDevice, stream);
-    if (e != cudaSuccess) return fail(2, err, err_len, cudaGetErrorString(e));
-    e = cudaStreamSynchronize(stream);  // chs is on this stack frame
-    if (e != cudaSuccess) return fail(2, err, err_len, cudaGetErrorString(e));
-    pd.world_laid_out = world;
+    pd.laid_out = true;
   }
 
   // The array keeps whatever the previous call left: flags, sequence counters
@@ -126,8 +144,10 @@ extern "C" int fairring_allreduce_f32_noalloc(float* const* bufs, int world, lon
   a.flags = kAdvanceSeq;
   if ((size_t)world * world * a.seg.qv * kVecBytes > kNaHalfBytes)
     return fail(1, err, err_len, "message does not fit the static staging area");
-  e = launchEmulated(KernelId::ONESHOT, reinterpret_cast<const ChannelDev*>(base + kOffChannels), a,
-                     world, /*blocks=*/2, stream);
+  e = launchEmulated(KernelId::ONESHOT,
+                     reinterpret_cast<const ChannelDev*>(base + kOffChannels +
+                                                         (size_t)(world - 2) * kNaTableBytes),
+                     a, world, /*blocks=*/2, stream);
   if (e != cudaSuccess) return fail(2, err, err_len, cudaGetErrorString(e));
 
   if (check) {

@@ -21,10 +21,10 @@ extern "C" {
 // that loads the library holds that array until the process exits.
 //
 //   bufs    host array of `world` device pointers (fp32, `numel` elements each,
-//           on the current device; the buffers must not overlap)
+//           on the current device -- checked; the buffers must not overlap)
 //   world   2..8
 //   numel   1..4096
-//   stream  a cudaStream_t (0 for the default stream)
+//   stream  a cudaStream_t of the current device (0 for the default stream)
 //   check   non-zero: wait for the stream and report a device-side time-out
 //   err     optional buffer that receives a message when the call fails
 //
@@ -33,8 +33,11 @@ extern "C" {
 // if `check` was set and a wait inside the kernel ran into its two-second limit.
 //
 // Calls no cudaMalloc/cudaFree and no allocating library routine.  The first
-// call on a device looks up the address of the static array and lays out the
-// bookkeeping in it; make that first call before any stream capture begins.
+// call on a device looks up the address of the static array, writes the
+// bookkeeping tables for every `world` from 2 to 8 into it and synchronises the
+// stream; make that first call before any stream capture begins.  Every later
+// call on that device, whatever its `world`, only clears the flags (a memset
+// on the stream) and launches the kernel.
 // All calls share the one array, and each call first clears the flags and
 // counters in it: two calls whose kernels overlap on the GPU (different
 // streams, no dependency) race with each other.  Issue them on one stream, or

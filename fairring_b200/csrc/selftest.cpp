@@ -3,17 +3,26 @@
 // runs the same collectives through its own CpuEngine on POSIX shared memory.
 // Gives fast, exhaustive coverage of groupings, rank numberings, slicing and
 // the double-buffered staging without spawning processes.
+//
+// Built twice: into the Python module (bindSelfTest), and, with
+// -DFR_SELFTEST_STANDALONE, as a plain program that runs the same bodies under
+// a thread sanitizer (tests/test_sanitizer.py): the command queue and the
+// shared-memory signalling are the host code whose races a test on results
+// alone would not see.
+#ifndef FR_SELFTEST_STANDALONE
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
+#endif
 
 #include <cmath>
+#include <cstdio>
 #include <condition_variable>
 #include <map>
 #include <mutex>
 #include <thread>
 
+#include "command_queue.h"
 #include "cpu_path.h"
-#include "engine.h"
 #include "kvstore.h"
 
 namespace fairring {
@@ -150,6 +159,7 @@ int64_t commandQueueSelfTest(int producers, int items_per_producer) {
   return bad;
 }
 
+#ifndef FR_SELFTEST_STANDALONE
 void bindSelfTest(pybind11::module_& m) {
   namespace py = pybind11;
   m.def("cpu_self_test", &cpuSelfTest, py::arg("world"), py::arg("gpus_per_machine"),
@@ -160,4 +170,20 @@ void bindSelfTest(pybind11::module_& m) {
         py::arg("items_per_producer") = 10000, py::call_guard<py::gil_scoped_release>());
 }
 
+#endif
+
 }  // namespace fairring
+
+#ifdef FR_SELFTEST_STANDALONE
+int main() {
+  using namespace fairring;
+  int64_t bad = commandQueueSelfTest(4, 20000);
+  std::printf("command queue: %lld violations\n", (long long)bad);
+  for (int gpm : {4, 2, 1}) {
+    const int64_t b = cpuSelfTest(4, gpm, false, {1, 37, 1000, 70001}, 1 << 20, 64 << 10, 1024, false);
+    std::printf("host all-reduce, 4 ranks in groups of %d: %lld mismatches\n", gpm, (long long)b);
+    bad += b;
+  }
+  return bad == 0 ? 0 : 1;
+}
+#endif

@@ -67,6 +67,34 @@ def _suite(rank, world, check_ddp):
     for i, b in enumerate(bufs):
         assert float(b[0]) == sum(r + i for r in range(world)) and float(b[-1]) == float(b[0])
 
+    # far more collectives in flight than any fixed pool of events could hold:
+    # every Work keeps its own completion event until it is destroyed
+    if check_ddp:
+        many = [torch.full((257,), float(rank + i % 7), device=dev) for i in range(1500)]
+        works = [dist.all_reduce(b, async_op=True) for b in many]
+        for w in works:
+            w.wait()
+        torch.cuda.synchronize()
+        for i, b in enumerate(many):
+            assert float(b[0]) == sum(r + i % 7 for r in range(world)) and float(b[-1]) == float(b[0])
+        del many, works
+        # a small blocking all_reduce runs on the caller's own stream
+        before = be.stats()["gpu_inline_collectives"]
+        small = torch.full((1000,), float(rank + 1), device=dev)
+        dist.all_reduce(small)
+        assert float(small[0]) == world * (world + 1) / 2
+        assert be.stats()["gpu_inline_collectives"] == before + 1
+        # symmetric memory is handed back: freed here, unmapped at the next allocation
+        tmp = be.symmetric_empty(1 << 20, torch.float32)
+        regions = be.stats()["symmetric_regions"]
+        del tmp
+        assert be.stats()["symmetric_pending_release"] == 1
+        tmp2 = be.symmetric_empty(1 << 18, torch.float32)
+        assert be.stats()["symmetric_pending_release"] == 0
+        assert be.stats()["symmetric_regions"] == regions
+        del tmp2
+        assert be.release_symmetric() == 1
+
     # a big ordinary tensor (the pipelined kernel when enabled), odd length
     x = seeded(12_000_001, torch.float32, rank, 9).to(dev)
     dist.all_reduce(x)

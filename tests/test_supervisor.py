@@ -59,3 +59,16 @@ def test_a_bad_child_fails_the_run_and_stops_the_others(bad, needle):
         recv_from_connections_and_join_processes(pairs, timeout=60)
     assert time.time() - t0 < 30
     assert not any(p.is_alive() for p, _ in pairs)
+
+
+def test_bench_tools_have_help():
+    """The command-line tools under fairring_b200.bench parse their arguments
+    without a GPU."""
+    import subprocess
+    import sys
+
+    for mod in ("kernel_probe", "sweep", "tune", "launch", "ddp_breakdown"):
+        out = subprocess.run([sys.executable, "-m", f"fairring_b200.bench.{mod}", "--help"],
+                             capture_output=True, text=True, timeout=120)
+        assert out.returncode == 0, (mod, out.stderr[-500:])
+        assert "usage" in out.stdout.lower()
