@@ -192,6 +192,51 @@ bool WorkFairring::wait(std::chrono::milliseconds timeout) {
 }
 
 // ---------------------------------------------------------------------------
+// MultiWork
+// ---------------------------------------------------------------------------
+bool MultiWorkFairring::isCompleted() {
+  for (auto& p : parts_)
+    if (!p->isCompleted()) return false;
+  return true;
+}
+bool MultiWorkFairring::isSuccess() const {
+  for (auto& p : parts_)
+    if (!p->isSuccess()) return false;
+  return true;
+}
+std::exception_ptr MultiWorkFairring::exception() const {
+  for (auto& p : parts_)
+    if (p->exception()) return p->exception();
+  return nullptr;
+}
+bool MultiWorkFairring::wait(std::chrono::milliseconds timeout) {
+  for (auto& p : parts_) p->wait(timeout);
+  return true;
+}
+void MultiWorkFairring::abort() {
+  for (auto& p : parts_) p->abort();
+}
+c10::intrusive_ptr<c10::ivalue::Future> MultiWorkFairring::getFuture() {
+  std::lock_guard<std::mutex> lk(mu_);
+  if (!future_) {
+    std::vector<c10::Device> devs;
+    std::vector<c10::cuda::CUDAStream> streams;
+    for (auto& p : parts_) {
+      const c10::DeviceIndex di = static_cast<c10::DeviceIndex>(p->device());
+      devs.emplace_back(at::kCUDA, di);
+      streams.push_back(c10::cuda::getStreamFromExternal(p->joinStream(), di));
+    }
+    future_ = c10::make_intrusive<c10::ivalue::Future>(
+        c10::ListType::create(c10::TensorType::get()), devs);
+    // The Future records one event per device on that device's current
+    // stream: make those the streams the collective finishes on.
+    c10::cuda::CUDAMultiStreamGuard g(streams);
+    future_->markCompleted(c10::IValue(result_));
+  }
+  return future_;
+}
+
+// ---------------------------------------------------------------------------
 // Backend
 // ---------------------------------------------------------------------------
 BackendFairring::BackendFairring(c10::intrusive_ptr<c10d::Store> store, int rank, int size,
@@ -210,6 +255,15 @@ BackendFairring::~BackendFairring() {
 
 void BackendFairring::shutdown() {
   std::lock_guard<std::mutex> lk(mu_);
+  if (!multi_engines_.empty()) {
+    // Tearing an engine down is collective over all (rank, GPU) pairs: the
+    // engines of this process must go down side by side.
+    std::vector<std::thread> ts;
+    for (auto& e : multi_engines_) ts.emplace_back([&e] { e.reset(); });
+    for (auto& t : ts) t.join();
+    multi_engines_.clear();
+    multi_devices_.clear();
+  }
   engine_.reset();
   cpu_engine_.reset();
   for (auto& kv : delegates_) {
@@ -246,12 +300,24 @@ const Deployment& BackendFairring::ensureDeployment() {
 }
 
 std::shared_ptr<Engine> BackendFairring::ensureEngine(int device) {
+  TORCH_CHECK(multi_engines_.empty(), "fairring: this process group serves several GPUs per process "
+              "(one tensor per GPU in every call); single-tensor collectives are not available on it");
   if (engine_) {
     TORCH_CHECK(device == engine_device_, "fairring: this process group already serves cuda:",
                 engine_device_, "; one GPU per process");
     return engine_;
   }
   const Deployment& dep = ensureDeployment();
+  const EngineConfig cfg = engineConfig();
+  c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+  engine_ = std::make_shared<Engine>(std::make_shared<StoreAdapter>(store_, "fairring/gpu/"),
+                                     dep.topo, device, cfg);
+  engine_device_ = device;
+  if (getRank() == 0) LOG(WARNING) << "fairring: " << engine_->describe();
+  return engine_;
+}
+
+EngineConfig BackendFairring::engineConfig() const {
   EngineConfig cfg;
   cfg.total_memory = options_->max_memory_allocated_in_bytes;
   cfg.slice_bytes = options_->slice_size_in_bytes;
@@ -285,12 +351,103 @@ std::shared_ptr<Engine> BackendFairring::ensureEngine(int device) {
   cfg.direct_max_slices = (int32_t)options_->direct_max_slices;
   cfg.direct_min_slice_bytes = options_->direct_min_slice_bytes;
   cfg.bootstrap_timeout = options_->timeout;
-  c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
-  engine_ = std::make_shared<Engine>(std::make_shared<StoreAdapter>(store_, "fairring/gpu/"),
-                                     dep.topo, device, cfg);
-  engine_device_ = device;
-  if (getRank() == 0) LOG(WARNING) << "fairring: " << engine_->describe();
-  return engine_;
+  return cfg;
+}
+
+void BackendFairring::ensureEngines(const std::vector<int>& devices) {
+  if (!multi_engines_.empty()) {
+    TORCH_CHECK(devices == multi_devices_, "fairring: every call must name the same GPUs in the "
+                "same order as the first one");
+    return;
+  }
+  TORCH_CHECK(!engine_, "fairring: this process group already serves one GPU per process");
+  const Deployment& dep = ensureDeployment();
+  TORCH_CHECK(dep.single_host, "fairring: several GPUs per process need all ranks on one NVSwitch host");
+  const int nd = (int)devices.size();
+  const int world = getSize() * nd;
+  TORCH_CHECK(world <= kMaxRanks, "fairring: ", getSize(), " processes x ", nd,
+              " GPUs exceed the ", kMaxRanks, " ranks of the peer-memory path");
+  int gpm = options_->gpus_per_machine > 0 ? (int)options_->gpus_per_machine : world;
+  TORCH_CHECK(world % gpm == 0, "fairring: FAIRRING_GPUS_PER_MACHINE must divide ", world);
+  EngineConfig cfg = engineConfig();
+  cfg.command_thread = false;
+  cfg.inline_small = false;
+  // Every engine's constructor is a collective over all (rank, GPU) pairs, so
+  // the engines of this process are built side by side, one thread each.
+  std::vector<std::shared_ptr<Engine>> built(nd);
+  std::vector<std::string> errors(nd);
+  std::vector<std::thread> ts;
+  for (int i = 0; i < nd; ++i) {
+    ts.emplace_back([&, i] {
+      try {
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(devices[i]));
+        const Topo topo = makeTopo(world, gpm, options_->favorable_layout, getRank() * nd + i);
+        built[i] = std::make_shared<Engine>(std::make_shared<StoreAdapter>(store_, "fairring/gpu/"),
+                                            topo, devices[i], cfg);
+      } catch (const std::exception& e) {
+        errors[i] = e.what();
+      }
+    });
+  }
+  for (auto& t : ts) t.join();
+  for (int i = 0; i < nd; ++i)
+    TORCH_CHECK(errors[i].empty(), "fairring: engine for cuda:", devices[i], " failed: ", errors[i]);
+  multi_engines_ = std::move(built);
+  multi_devices_ = devices;
+  if (getRank() == 0) LOG(WARNING) << "fairring: " << multi_engines_[0]->describe() << " (" << nd << " GPUs per process)";
+}
+
+// One tensor per GPU of this process (fairring/machine.cc:177-202 of the
+// reference): the same all_reduce runs on every GPU's engine; the returned
+// Work waits for all of them.
+c10::intrusive_ptr<c10d::Work> BackendFairring::allreduceMulti(std::vector<at::Tensor>& tensors,
+                                                               const c10d::AllreduceOptions& opts) {
+  std::vector<int> devices;
+  for (const auto& t : tensors) {
+    TORCH_CHECK(t.is_cuda() && !t.is_sparse(), "fairring: a multi-GPU all_reduce takes dense CUDA tensors");
+    TORCH_CHECK(t.numel() == tensors[0].numel() && t.scalar_type() == tensors[0].scalar_type(),
+                "fairring: the tensors of a multi-GPU all_reduce must agree in size and dtype");
+    checkDense(t, "the all_reduce tensor");
+    for (int d : devices) TORCH_CHECK(d != t.get_device(), "fairring: one tensor per GPU");
+    devices.push_back(t.get_device());
+  }
+  Mapped m = mapOp(tensors[0], opts.reduceOp);
+  TORCH_CHECK(m.ok, "fairring: this reduction is not available for several GPUs per process");
+  std::lock_guard<std::mutex> lk(mu_);
+  ensureEngines(devices);
+  if (m.scale != 1.0f) m.scale = 1.0f / (float)(getSize() * (int)devices.size());  // AVG over all GPUs
+  std::vector<c10::intrusive_ptr<WorkFairring>> parts;
+  for (size_t i = 0; i < tensors.size(); ++i) {
+    auto& engine = multi_engines_[i];
+    const c10::DeviceIndex di = static_cast<c10::DeviceIndex>(devices[i]);
+    c10::cuda::CUDAGuard guard(di);
+    CollectiveDesc d;
+    d.kind = CollKind::ALLREDUCE;
+    d.in = d.out = tensors[i].data_ptr();
+    d.numel = tensors[i].numel();
+    d.io = d.wire = m.dtype;
+    d.op = m.op;
+    d.scale = m.scale;
+    auto work = c10::make_intrusive<WorkFairring>(c10d::OpType::ALLREDUCE, engine, (int)di,
+                                                  std::vector<at::Tensor>{tensors[i]},
+                                                  options_->blocking_wait, options_->timeout);
+    cudaEvent_t after = engine->begin(c10::cuda::getCurrentCUDAStream(di).stream());
+    try {
+      std::vector<cudaStream_t> used;
+      cudaStream_t s = engine->run(d, after, &used);
+      engine->releaseEvent(after);
+      for (cudaStream_t u : used)
+        c10::cuda::CUDACachingAllocator::recordStream(tensors[i].storage().data_ptr(),
+                                                      c10::cuda::getStreamFromExternal(u, di));
+      work->markEnqueued(engine->begin(s), s);
+    } catch (const Error& e) {
+      engine->releaseEvent(after);
+      TORCH_CHECK(false, e.what());
+    }
+    parts.push_back(std::move(work));
+  }
+  ++seq_;
+  return c10::make_intrusive<MultiWorkFairring>(c10d::OpType::ALLREDUCE, std::move(parts), tensors);
 }
 
 CpuEngine& BackendFairring::ensureCpuEngine() {
@@ -415,7 +572,8 @@ c10::intrusive_ptr<c10d::Work> BackendFairring::runGpu(c10d::OpType type, const 
 // ---- all_reduce ------------------------------------------------------------
 c10::intrusive_ptr<c10d::Work> BackendFairring::allreduce(std::vector<at::Tensor>& tensors,
                                                           const c10d::AllreduceOptions& opts) {
-  TORCH_CHECK(tensors.size() == 1, "fairring: one tensor per call (one GPU per process)");
+  TORCH_CHECK(!tensors.empty(), "fairring: empty tensor list");
+  if (tensors.size() > 1) return allreduceMulti(tensors, opts);
   at::Tensor& t = tensors[0];
   TORCH_CHECK(!t.is_sparse(), "fairring: sparse tensors are not supported");
   const Mapped m = mapOp(t, opts.reduceOp);

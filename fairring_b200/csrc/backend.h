@@ -101,6 +101,9 @@ class WorkFairring : public c10d::Work {
   // Called by the enqueueing code (caller's thread, or the command thread).
   void markEnqueued(cudaEvent_t done, cudaStream_t join);
   void markFailed(std::exception_ptr e);
+  // Where the collective finishes (valid once enqueued).
+  int device() const { return device_; }
+  cudaStream_t joinStream() const { return join_; }
 
  private:
   void waitEnqueued();
@@ -117,6 +120,32 @@ class WorkFairring : public c10d::Work {
   cudaEvent_t done_ = nullptr;
   cudaStream_t join_ = nullptr;
   std::exception_ptr error_;
+  c10::intrusive_ptr<c10::ivalue::Future> future_;
+};
+
+// One collective over several GPUs of this process: one WorkFairring per GPU,
+// waited for together.  Counterpart of mergeMultiDeviceFutures in the reference
+// (fairring/machine.cc:251-288), which merges the per-device futures on a merge
+// stream per device; here waiting is an event wait on each device's current
+// stream and the merged Future is completed under all the finishing streams.
+class MultiWorkFairring : public c10d::Work {
+ public:
+  MultiWorkFairring(c10d::OpType op, std::vector<c10::intrusive_ptr<WorkFairring>> parts,
+                    std::vector<at::Tensor> result)
+      : c10d::Work(-1, op), parts_(std::move(parts)), result_(std::move(result)) {}
+  bool isCompleted() override;
+  bool isSuccess() const override;
+  std::exception_ptr exception() const override;
+  std::vector<at::Tensor> result() override { return result_; }
+  void synchronize() override { wait(kNoTimeout); }
+  bool wait(std::chrono::milliseconds timeout = kNoTimeout) override;
+  void abort() override;
+  c10::intrusive_ptr<c10::ivalue::Future> getFuture() override;
+
+ private:
+  std::vector<c10::intrusive_ptr<WorkFairring>> parts_;
+  std::vector<at::Tensor> result_;
+  std::mutex mu_;
   c10::intrusive_ptr<c10::ivalue::Future> future_;
 };
 
@@ -230,12 +259,19 @@ class BackendFairring : public c10d::Backend {
   c10::intrusive_ptr<c10d::Backend> delegateFor(const std::vector<at::Tensor>& t);
   const Deployment& ensureDeployment();
   std::shared_ptr<Engine> ensureEngine(int device);
+  EngineConfig engineConfig() const;
   CpuEngine& ensureCpuEngine();
   c10::intrusive_ptr<c10d::Work> runGpu(c10d::OpType type, const CollectiveDesc& d,
                                         std::vector<at::Tensor> keep,
                                         std::vector<at::Tensor> result,
                                         std::function<void()> epilogue);
   c10::intrusive_ptr<c10d::Work> completedWork(c10d::OpType type, std::vector<at::Tensor> result);
+  // Several GPUs in this process (one tensor per GPU in a call): one engine per
+  // GPU, built together on first use; every (rank, GPU) pair is a rank of the
+  // peer-memory world.
+  void ensureEngines(const std::vector<int>& devices);
+  c10::intrusive_ptr<c10d::Work> allreduceMulti(std::vector<at::Tensor>& tensors,
+                                                const c10d::AllreduceOptions& opts);
 
   c10::intrusive_ptr<c10d::Store> store_;
   c10::intrusive_ptr<OptionsFairring> options_;
@@ -245,6 +281,8 @@ class BackendFairring : public c10d::Backend {
   Deployment deployment_;
   std::shared_ptr<Engine> engine_;
   int engine_device_ = -1;
+  std::vector<std::shared_ptr<Engine>> multi_engines_;  // multi-GPU-per-process mode
+  std::vector<int> multi_devices_;
   std::unique_ptr<CpuEngine> cpu_engine_;
   std::map<std::string, c10::intrusive_ptr<c10d::Backend>> delegates_;
   uint64_t seq_ = 0;

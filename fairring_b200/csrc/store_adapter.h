@@ -3,7 +3,9 @@
 
 #include <torch/csrc/distributed/c10d/Store.hpp>
 
+#include <chrono>
 #include <string>
+#include <thread>
 #include <utility>
 #include <vector>
 
@@ -18,7 +20,21 @@ class StoreAdapter : public KvStore {
   void set(const std::string& key, const std::vector<uint8_t>& value) override {
     store_->set(prefix_ + key, value);
   }
-  std::vector<uint8_t> get(const std::string& key) override { return store_->get(prefix_ + key); }
+  // Polls until the key exists instead of blocking inside the store: a store
+  // client serialises its operations, and with several GPUs per process two
+  // ranks share one client -- a blocking get of rank A would lock out the very
+  // set of rank B that it waits for.
+  std::vector<uint8_t> get(const std::string& key) override {
+    const std::string k = prefix_ + key;
+    const auto limit = store_->getTimeout();
+    const auto t0 = std::chrono::steady_clock::now();
+    while (!store_->check({k})) {
+      FR_CHECK(limit.count() <= 0 || std::chrono::steady_clock::now() - t0 < limit, "store key '", k,
+               "' never appeared: a rank is missing");
+      std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+    return store_->get(k);
+  }
   int64_t add(const std::string& key, int64_t delta) override {
     return store_->add(prefix_ + key, delta);
   }

@@ -348,3 +348,57 @@ def test_reference_sequence_arm(gpm):
     expect = 3.0 * 2 * 2  # (1 + 2), then doubled twice
     for first, last in res[0]:
         assert first == expect and last == expect, res[0]
+
+
+# --- several GPUs in one process: one tensor per GPU, one merged Work -----------------
+def _gpus_in_one_process(rank, world, per_proc):
+    import torch.distributed as dist
+
+    import fairring
+
+    from datetime import timedelta
+
+    devs = [torch.device("cuda", rank * per_proc + i) for i in range(per_proc)]
+    torch.cuda.set_device(devs[0])
+    dist.init_process_group("fairring", rank=rank, world_size=world, timeout=timedelta(seconds=60))
+    be = fairring.get_backend(device="cuda")
+    total = world * per_proc
+    out = []
+    for n in (1000, 3_000_001):
+        ts = [torch.full((n,), float(rank * per_proc + i + 1), device=d) for i, d in enumerate(devs)]
+        w = be.allreduce(ts)
+        w.wait()
+        for d in devs:
+            torch.cuda.synchronize(d)
+        out.append([float(t[0]) for t in ts] + [float(t[-1]) for t in ts])
+    # the merged Future (what a DDP-style consumer would chain on)
+    ts = [torch.full((70_000,), 2.0, device=d) for d in devs]
+    fut = be.allreduce(ts).get_future()
+    fut.wait()
+    for d in devs:
+        torch.cuda.synchronize(d)
+    out.append([float(t[0]) for t in fut.value()])
+    assert total * (total + 1) / 2 == out[0][0]
+    dist.destroy_process_group()
+    return out
+
+
+def test_two_gpus_in_one_process():
+    if _ngpu() < 2:
+        pytest.skip("needs at least two GPUs")
+    env = {"FAIRRING_TOTAL_MEMORY": str(64 << 20), "FAIRRING_DEVICE_TIMEOUT_MS": "5000"}
+    res = run_ranks(_gpus_in_one_process, 1, env=env, args=(2,), timeout=150)
+    small, big, fut = res[0]
+    assert all(v == 3.0 for v in small) and all(v == 3.0 for v in big)
+    assert fut == [4.0, 4.0]
+
+
+def test_two_processes_of_two_gpus():
+    if _ngpu() < 4:
+        pytest.skip("needs at least four GPUs")
+    env = {"FAIRRING_TOTAL_MEMORY": str(64 << 20), "FAIRRING_DEVICE_TIMEOUT_MS": "5000"}
+    res = run_ranks(_gpus_in_one_process, 2, env=env, args=(2,), timeout=240)
+    for r in (0, 1):
+        small, big, fut = res[r]
+        assert all(v == 10.0 for v in small) and all(v == 10.0 for v in big)
+        assert fut == [8.0, 8.0]
