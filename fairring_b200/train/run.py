@@ -100,7 +100,9 @@ def main(argv=None) -> int:
     wire_name = args.wire if args.wire != "auto" else ("fp16" if args.workload == "resnet50" else "fp32")
     wire = {"fp32": None, "bf16": torch.bfloat16, "fp16": torch.float16}[wire_name]
 
-    if args.impl == "fairring" and args.ddp == "flat":
+    if args.ddp == "flat" and (args.impl == "fairring" or wire is None):
+        # On NCCL the flat buffers are averaged with plain all_reduce calls (no
+        # fused wire cast): the two arms then differ in the backend only.
         ddp = FlatDataParallel(model, bucket_cap_mb=args.bucket_mb, wire_dtype=wire)
         opt = FlatAdamW(ddp.flat_param, ddp.flat_grad, lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
     else:
