@@ -216,7 +216,7 @@ def main():
         ddp = FlatDataParallel(model, bucket_cap_mb=args.bucket_mb, wire_dtype=wire,
                                bf16_shadow=not args.no_shadow)
         opt = FlatAdamW(ddp.flat_param, ddp.flat_grad, lr=lr, betas=betas, weight_decay=wd,
-                        shadow=ddp.flat_shadow)
+                        shadow=ddp.flat_shadow, overlap=ddp)
         parallel_desc = "flat-dp + fused AdamW" + ("" if args.no_shadow else " + bf16 shadow weights")
     else:
         from torch.nn.parallel import DistributedDataParallel as DDP
@@ -370,6 +370,9 @@ def main():
         }
         if check is not None:
             out["check"] = check
+        if backend is not None:
+            out["kernels_launched"] = {k: int(v) for k, v in backend.stats().items()
+                                       if k.startswith("launch_") and v}
         print(json.dumps(out), flush=True)
     sync_all()
     if reference:

@@ -30,6 +30,8 @@ FAIRRING_SM_BUDGET             SMs the collectives may occupy at once (default 6
                                leave the GPU to backward
 FAIRRING_LL_MAX                largest message (bytes) for the flag-in-data kernel (default 32 KiB;
                                0 turns it off); FAIRRING_LL_CHANNELS channels carry its areas
+FAIRRING_LL2_MAX               largest message (bytes) for its two-shot form (default 1 MiB; the
+                               areas shrink it when the memory budget is small)
 FAIRRING_INLINE_SMALL          1 (default): a blocking all_reduce that fits that kernel runs on the
                                caller's own stream
 FAIRRING_ONESHOT_MAX           largest message (bytes) for the one-shot kernel
@@ -111,6 +113,7 @@ def _env_int(name: str, default: int) -> int:
 # Option name -> the environment variable that overrides it.
 _TUNABLES = {
     "ll_max_bytes": "FAIRRING_LL_MAX",
+    "ll2_max_bytes": "FAIRRING_LL2_MAX",
     "oneshot_max_bytes": "FAIRRING_ONESHOT_MAX",
     "nvls_oneshot_max_bytes": "FAIRRING_NVLS_ONESHOT_MAX",
     "pipe_min_bytes": "FAIRRING_PIPE_MIN",
@@ -167,6 +170,7 @@ def options_from_env(timeout: timedelta | None = None, world: int = 0) -> "_C.Op
     opts.sm_budget = _env_int("FAIRRING_SM_BUDGET", opts.sm_budget)
     opts.oneshot_max_bytes = _env_int("FAIRRING_ONESHOT_MAX", opts.oneshot_max_bytes)
     opts.ll_max_bytes = _env_int("FAIRRING_LL_MAX", opts.ll_max_bytes)
+    opts.ll2_max_bytes = _env_int("FAIRRING_LL2_MAX", opts.ll2_max_bytes)
     opts.ll_channels = _env_int("FAIRRING_LL_CHANNELS", opts.ll_channels)
     opts.inline_small = os.environ.get("FAIRRING_INLINE_SMALL", "1") == "1"
     opts.direct_unroll = _env_int("FAIRRING_DIRECT_UNROLL", opts.direct_unroll)

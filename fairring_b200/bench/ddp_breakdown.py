@@ -33,6 +33,8 @@ def main(argv=None) -> int:
     ap.add_argument("--preset", choices=["flagship", "tiny"], default="flagship")
     ap.add_argument("--configs", default="16x2,8x2,8x1,16x1,24x1,32x2")
     ap.add_argument("--unrolls", default="8")
+    ap.add_argument("--no-tail-overlap", action="store_true",
+                    help="wait for the last bucket at the end of backward instead of inside the optimizer")
     ap.add_argument("--json", default="")
     args = ap.parse_args(argv)
 
@@ -56,7 +58,7 @@ def main(argv=None) -> int:
     model = DecoderLM(cfg).to(dev)
     ddp = FlatDataParallel(model, bf16_shadow=True)
     opt = FlatAdamW(ddp.flat_param, ddp.flat_grad, lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1,
-                    shadow=ddp.flat_shadow)
+                    shadow=ddp.flat_shadow, overlap=None if args.no_tail_overlap else ddp)
     be = fairring_b200.get_backend(device="cuda") if world > 1 else None
     B, S = 8, cfg.seq_len
     tok = torch.randint(0, cfg.vocab, (B, S + 1), generator=torch.Generator().manual_seed(rank)).to(dev)

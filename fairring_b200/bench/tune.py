@@ -31,7 +31,8 @@ from pathlib import Path
 import torch
 import torch.distributed as dist
 
-ALGO = {"auto": 0, "oneshot": 1, "twoshot": 2, "hier": 3, "nvls": 4, "nvls_oneshot": 5, "pipe": 6, "ll": 7}
+ALGO = {"auto": 0, "oneshot": 1, "twoshot": 2, "hier": 3, "nvls": 4, "nvls_oneshot": 5, "pipe": 6, "ll": 7,
+        "ll2": 8}
 
 
 def main(argv=None) -> int:
@@ -51,6 +52,7 @@ def main(argv=None) -> int:
     os.environ.setdefault("FAIRRING_SM_BUDGET", "148")
     os.environ.setdefault("FAIRRING_PARALLELISM", "4")
     os.environ.setdefault("FAIRRING_LL_MAX", str(256 << 10))
+    os.environ.setdefault("FAIRRING_LL2_MAX", str(4 << 20))
     os.environ.setdefault("FAIRRING_PIPE_SLOTS", "8")
     os.environ["FAIRRING_TUNING_TABLE"] = "off"
     import fairring_b200
@@ -171,6 +173,7 @@ def main(argv=None) -> int:
         sizes = [1 << k for k in range(12, 23)]
         variants = [("ll inline", dict(algo=ALGO["ll"], inline_small=1, ll_max_bytes=256 << 10), 256 << 10),
                     ("ll side-stream", dict(algo=ALGO["ll"], inline_small=0, ll_max_bytes=256 << 10), 256 << 10),
+                    ("ll2", dict(algo=ALGO["ll2"], ll_max_bytes=0, ll2_max_bytes=4 << 20), 4 << 20),
                     ("oneshot", dict(algo=ALGO["oneshot"], ll_max_bytes=0), 1 << 20),
                     ("nvls_oneshot", dict(algo=ALGO["nvls_oneshot"], ll_max_bytes=0), 4 << 20),
                     ("nvls twoshot", dict(algo=ALGO["nvls"], ll_max_bytes=0), 4 << 20),
@@ -183,7 +186,8 @@ def main(argv=None) -> int:
                 us, bw = measure(arena, size)
                 add("small", {"variant": name}, size, us, bw)
             arena.normal_()
-        setopt(algo=ALGO["auto"], ll_max_bytes=32 << 10, inline_small=1, pipe_min_bytes=512 << 10)
+        setopt(algo=ALGO["auto"], ll_max_bytes=32 << 10, ll2_max_bytes=1 << 20, inline_small=1,
+               pipe_min_bytes=512 << 10)
         be.check_health()
 
     if rank == 0:
@@ -215,12 +219,14 @@ def derive_table(rows, world):
         if r.get("part") == "small":
             small.setdefault(r["bytes"], {})[r["variant"]] = r["us"]
     best = {size: min(v, key=v.get) for size, v in small.items()}
-    ll_max = max([s for s, b in best.items() if b.startswith("ll")], default=0)
+    ll_max = max([s for s, b in best.items() if b.startswith("ll ")], default=0)
+    ll2_max = max([s for s, b in best.items() if b == "ll2"], default=0)
     oneshot_max = max([s for s, b in best.items() if b == "oneshot"], default=0)
     nvls1_max = max([s for s, b in best.items() if b == "nvls_oneshot"], default=0)
     pipe_min = min([s for s, b in best.items() if b == "pipe"], default=0)
     if ll_max:
         table["ll_max_bytes"] = ll_max
+    table["ll2_max_bytes"] = ll2_max
     table["oneshot_max_bytes"] = max(oneshot_max, ll_max)
     table["nvls_oneshot_max_bytes"] = max(nvls1_max, table["oneshot_max_bytes"])
     if pipe_min:

@@ -326,6 +326,7 @@ EngineConfig BackendFairring::engineConfig() const {
   cfg.sm_budget = (int32_t)options_->sm_budget;
   cfg.oneshot_max_bytes = options_->oneshot_max_bytes;
   cfg.ll_max_bytes = options_->ll_max_bytes;
+  cfg.ll2_max_bytes = options_->ll2_max_bytes;
   cfg.ll_channels = (int32_t)options_->ll_channels;
   cfg.inline_small = options_->inline_small;
   cfg.direct_unroll = (int32_t)options_->direct_unroll;

@@ -49,6 +49,7 @@ struct OptionsFairring : c10d::Backend::Options {
   int64_t sm_budget = 64;
   int64_t oneshot_max_bytes = 256 << 10;
   int64_t ll_max_bytes = 32 << 10;   // flag-in-data kernel up to this size; 0: off
+  int64_t ll2_max_bytes = 1 << 20;   // ... and its two-shot form up to this size; 0: off
   int64_t ll_channels = 4;
   bool inline_small = true;          // blocking small all_reduce runs on the caller's stream
   int64_t direct_unroll = 8;

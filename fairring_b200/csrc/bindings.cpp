@@ -72,6 +72,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("sm_budget", &OptionsFairring::sm_budget)
       .def_readwrite("oneshot_max_bytes", &OptionsFairring::oneshot_max_bytes)
       .def_readwrite("ll_max_bytes", &OptionsFairring::ll_max_bytes)
+      .def_readwrite("ll2_max_bytes", &OptionsFairring::ll2_max_bytes)
       .def_readwrite("ll_channels", &OptionsFairring::ll_channels)
       .def_readwrite("inline_small", &OptionsFairring::inline_small)
       .def_readwrite("direct_unroll", &OptionsFairring::direct_unroll)

@@ -75,7 +75,9 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
   auto i32 = bopt.dtype(at::kInt);
   std::vector<at::Tensor> staging, flags, seqs, outs, lls;
   // flag-in-data areas: two halves of [rank][unit] 16-byte words
-  const int64_t ll_half = (int64_t)kMaxRanks * roundUp(ceilDiv(algo == "ll" ? n_in * dtypeSize(io) : 8, 8), 64) * 16;
+  const int64_t ll_msg = (algo == "ll" || algo == "ll2") ? n_in * dtypeSize(io) : 8;
+  const int64_t ll_half = std::max<int64_t>((int64_t)kMaxRanks * roundUp(ceilDiv(ll_msg, 8), 64) * 16,
+                                            4 * ll_msg + 32 * kMaxRanks * 64);
   for (int r = 0; r < W; ++r) {
     lls.push_back(at::zeros({2 * ll_half}, u8));
     staging.push_back(at::zeros({2 * half_bytes}, u8));
@@ -163,9 +165,10 @@ std::tuple<std::vector<at::Tensor>, at::Tensor> emulatedCollective(
                                        static_cast<const ChannelDev*>(chs_dev.data_ptr()), a, W,
                                        (int)blocks, stream);
         TORCH_CHECK(e == cudaSuccess, "emulated direct launch failed: ", cudaGetErrorString(e));
-      } else if (algo == "ll") {
-        TORCH_CHECK(io == wire, "the flag-in-data kernel carries the tensor's own dtype");
-        launchAll(KernelId::LL_ONESHOT, allreduceSeg(n_in, wes, W), 0, 0, kAdvanceSeq);
+      } else if (algo == "ll" || algo == "ll2") {
+        TORCH_CHECK(io == wire, "the flag-in-data kernels carry the tensor's own dtype");
+        launchAll(algo == "ll" ? KernelId::LL_ONESHOT : KernelId::LL_TWOSHOT,
+                  allreduceSeg(n_in, wes, W), 0, 0, kAdvanceSeq);
       } else if (algo == "oneshot") {
         const Seg s = allreduceSeg(n_in, wes, W);
         TORCH_CHECK((int64_t)W * W * s.qv * kVecBytes <= half_bytes, "message too large for one-shot");

@@ -23,16 +23,17 @@ const char* algoName(Algo a) {
     case Algo::NVLS_ONESHOT: return "nvls_oneshot";
     case Algo::PIPE: return "pipe";
     case Algo::LL: return "ll";
+    case Algo::LL2: return "ll2";
   }
   return "?";
 }
 
 Algo parseAlgo(const std::string& s) {
   for (Algo a : {Algo::AUTO, Algo::ONESHOT, Algo::TWOSHOT, Algo::HIER, Algo::NVLS, Algo::NVLS_ONESHOT,
-                 Algo::PIPE, Algo::LL})
+                 Algo::PIPE, Algo::LL, Algo::LL2})
     if (s == algoName(a)) return a;
   FR_CHECK(false, "unknown FAIRRING_ALGO '", s,
-           "' (auto, oneshot, twoshot, hier, nvls, nvls_oneshot, pipe, ll)");
+           "' (auto, oneshot, twoshot, hier, nvls, nvls_oneshot, pipe, ll, ll2)");
   return Algo::AUTO;
 }
 
@@ -69,13 +70,29 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
   const int budget = std::max(widest, std::min(sms, cfg_.sm_budget));
   const int max_channels = std::max(1, budget / widest);
   if (cfg_.parallelism > max_channels) cfg_.parallelism = max_channels;
-  // The flag-in-data areas come off the top of the budget (an eighth at most).
+  // The flag-in-data areas come off the top of the budget (a quarter at most):
+  // fewer channels first, then smaller messages.
   int64_t ll_total = 0;
   if (cfg_.ll_max_bytes > 0 && topo_.world > 1) {
     ll_channels_ = std::max(1, std::min(cfg_.ll_channels, cfg_.parallelism));
-    ll_half_bytes_ = (int64_t)kMaxRanks * roundUp(ceilDiv(cfg_.ll_max_bytes, 8), 64) * 16;
-    while (ll_channels_ > 1 && 2 * ll_half_bytes_ * ll_channels_ > cfg_.total_memory / 8) --ll_channels_;
-    if (2 * ll_half_bytes_ * ll_channels_ > cfg_.total_memory / 8) {
+    auto halfFor = [&](int64_t one, int64_t two) {
+      const int64_t a = (int64_t)kMaxRanks * roundUp(ceilDiv(one, 8), 64) * 16;
+      const int64_t b = roundUp(4 * two + 32 * kMaxRanks * 64, 4096);
+      return std::max(a, two > 0 ? b : 0);
+    };
+    ll_half_bytes_ = halfFor(cfg_.ll_max_bytes, cfg_.ll2_max_bytes);
+    const int64_t cap = cfg_.total_memory / 4;
+    while (ll_channels_ > 1 && 2 * ll_half_bytes_ * ll_channels_ > cap) --ll_channels_;
+    while (2 * ll_half_bytes_ > cap && (cfg_.ll2_max_bytes > 0 || cfg_.ll_max_bytes > 4096)) {
+      if (cfg_.ll2_max_bytes > cfg_.ll_max_bytes)
+        cfg_.ll2_max_bytes /= 2;
+      else if (cfg_.ll2_max_bytes > 0)
+        cfg_.ll2_max_bytes = 0;
+      else
+        cfg_.ll_max_bytes /= 2;
+      ll_half_bytes_ = halfFor(cfg_.ll_max_bytes, cfg_.ll2_max_bytes);
+    }
+    if (2 * ll_half_bytes_ > cap) {
       ll_channels_ = 0;
       ll_half_bytes_ = 0;
     }
@@ -525,7 +542,8 @@ std::vector<cudaStream_t> Engine::streams() const {
 
 std::string Engine::describe() const {
   std::ostringstream os;
-  os << "ll=" << (ll_channels_ > 0 ? cfg_.ll_max_bytes : 0) << "B/" << ll_channels_ << "ch "
+  os << "ll=" << (ll_channels_ > 0 ? cfg_.ll_max_bytes : 0) << "B+" << (ll_channels_ > 0 ? cfg_.ll2_max_bytes : 0)
+     << "B/" << ll_channels_ << "ch "
      << "world=" << topo_.world << " grouping=" << topo_.M << "x" << topo_.D
      << (topo_.favorable ? " (device-major ranks)" : " (machine-major ranks)")
      << " transport=" << alloc_->describe() << " nvls=" << (nvlsAvailable() ? "yes" : "no")
@@ -548,7 +566,7 @@ Algo Engine::chooseAllreduce(int64_t wire_bytes, DType wire, RedOp op) const {
   Algo a = cfg_.algo;
   if (a == Algo::ONESHOT && !oneshot_fits) a = Algo::AUTO;
   if ((a == Algo::NVLS || a == Algo::NVLS_ONESHOT) && !nvls_ok) a = Algo::AUTO;
-  if (a == Algo::PIPE || a == Algo::LL) a = Algo::AUTO;  // this message did not qualify for that kernel
+  if (a == Algo::PIPE || a == Algo::LL || a == Algo::LL2) a = Algo::AUTO;  // did not qualify for that kernel
   if (a == Algo::TWOSHOT && topo_.M > 1) a = Algo::HIER;
   if (a != Algo::AUTO) return a;
   if (wire_bytes <= cfg_.oneshot_max_bytes && oneshot_fits) return Algo::ONESHOT;
@@ -560,13 +578,20 @@ Algo Engine::chooseAllreduce(int64_t wire_bytes, DType wire, RedOp op) const {
   return Algo::TWOSHOT;
 }
 
-bool Engine::fitsInline(const CollectiveDesc& d) const {
-  if (!cfg_.inline_small || ll_channels_ == 0 || d.kind != CollKind::ALLREDUCE || d.io != d.wire)
-    return false;
-  if (cfg_.algo != Algo::AUTO && cfg_.algo != Algo::LL) return false;
-  if (cfg_.command_thread) return false;
+int Engine::llKind(const CollectiveDesc& d) const {
+  if (ll_channels_ == 0 || d.kind != CollKind::ALLREDUCE || d.io != d.wire || d.numel <= 0) return 0;
   const int64_t bytes = d.numel * dtypeSize(d.wire);
-  return bytes > 0 && bytes <= cfg_.ll_max_bytes;
+  const bool any = cfg_.algo == Algo::AUTO;
+  if ((any || cfg_.algo == Algo::LL) && bytes <= cfg_.ll_max_bytes) return 1;
+  if (any || cfg_.algo == Algo::LL2) {
+    const int64_t cu = ceilDiv(ceilDiv(bytes, 8), topo_.world);
+    if (bytes <= cfg_.ll2_max_bytes && 2 * (int64_t)topo_.world * cu * 16 <= ll_half_bytes_) return 2;
+  }
+  return 0;
+}
+
+bool Engine::fitsInline(const CollectiveDesc& d) const {
+  return cfg_.inline_small && !cfg_.command_thread && llKind(d) != 0;
 }
 
 void Engine::launchLL(Channel& ch, const CollectiveDesc& d, cudaStream_t stream) {
@@ -580,11 +605,11 @@ void Engine::launchLL(Channel& ch, const CollectiveDesc& d, cudaStream_t stream)
   a.flags = kAdvanceSeq;
   // Always the channel's full grid: every block keeps its own count of the
   // channel's collectives, so every launch on a channel must run every block.
-  cudaError_t e = launchCollective(KernelId::LL_ONESHOT, channels_dev_ + (&ch - channels_.data()), a,
-                                   cfg_.blocks, stream);
-  FR_CHECK(e == cudaSuccess, "launch of ll_allreduce failed: ", cudaGetErrorString(e));
-  ++stats_.launches[(size_t)KernelId::LL_ONESHOT];
-  if (cur_.launches == 0) cur_.first_kernel = (int32_t)KernelId::LL_ONESHOT;
+  const KernelId id = llKind(d) == 2 ? KernelId::LL_TWOSHOT : KernelId::LL_ONESHOT;
+  cudaError_t e = launchCollective(id, channels_dev_ + (&ch - channels_.data()), a, cfg_.blocks, stream);
+  FR_CHECK(e == cudaSuccess, "launch of ", kernelName(id), " failed: ", cudaGetErrorString(e));
+  ++stats_.launches[(size_t)id];
+  if (cur_.launches == 0) cur_.first_kernel = (int32_t)id;
   ++cur_.launches;
   ++stats_.slices;
   stats_.wire_bytes += (uint64_t)(d.numel * dtypeSize(d.wire));
@@ -652,6 +677,8 @@ void Engine::setOption(const std::string& name, int64_t v) {
     FR_CHECK(ll_channels_ == 0 || (int64_t)kMaxRanks * roundUp(ceilDiv(v, 8), 64) * 16 <= ll_half_bytes_,
              "ll_max_bytes beyond the areas allocated at start-up");
     cfg_.ll_max_bytes = v;
+  } else if (name == "ll2_max_bytes") {
+    cfg_.ll2_max_bytes = v;  // messages that do not fit the areas are refused per message
   } else if (name == "oneshot_max_bytes") {
     cfg_.oneshot_max_bytes = v;
   } else if (name == "nvls_oneshot_max_bytes") {
@@ -661,7 +688,7 @@ void Engine::setOption(const std::string& name, int64_t v) {
   } else if (name == "inline_small") {
     cfg_.inline_small = v != 0;
   } else if (name == "algo") {
-    FR_CHECK(v >= 0 && v <= (int64_t)Algo::LL, "algo out of range");
+    FR_CHECK(v >= 0 && v <= (int64_t)Algo::LL2, "algo out of range");
     cfg_.algo = (Algo)v;
   } else {
     FR_CHECK(false, "unknown engine option '", name, "'");
@@ -768,10 +795,7 @@ cudaStream_t Engine::run(const CollectiveDesc& d, cudaEvent_t after,
     }
   } finish{this, &used, t_begin, slices_before};
 
-  const bool ll_fits = ll_channels_ > 0 && d.kind == CollKind::ALLREDUCE && d.io == d.wire &&
-                       d.numel > 0 && d.numel * wes <= cfg_.ll_max_bytes &&
-                       (cfg_.algo == Algo::AUTO || cfg_.algo == Algo::LL);
-  if (ll_fits) {
+  if (llKind(d) != 0) {
     Channel& ch = take((int)(next_ll_++ % (uint64_t)ll_channels_));
     launchLL(ch, d, ch.stream);
   } else if (runDirect(d, take) || runPipe(d, take)) {

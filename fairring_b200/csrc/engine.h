@@ -32,7 +32,7 @@
 
 namespace fairring {
 
-enum class Algo : int32_t { AUTO = 0, ONESHOT, TWOSHOT, HIER, NVLS, NVLS_ONESHOT, PIPE, LL };
+enum class Algo : int32_t { AUTO = 0, ONESHOT, TWOSHOT, HIER, NVLS, NVLS_ONESHOT, PIPE, LL, LL2 };
 const char* algoName(Algo a);
 Algo parseAlgo(const std::string& s);
 
@@ -48,6 +48,9 @@ struct EngineConfig {
   // all); its areas (2 x 16 bytes per 8 bytes of message per rank, on up to
   // ll_channels channels) come off the top of the memory budget.  0: off.
   int64_t ll_max_bytes = 32 << 10;
+  // ... and up to ll2_max_bytes its two-shot form (reduce-scatter + all-gather
+  // in flag-in-data words), which needs 4 bytes of area per byte of message.
+  int64_t ll2_max_bytes = 1 << 20;
   int32_t ll_channels = 4;
   // A blocking all_reduce (async_op=False) that fits the flag-in-data kernel is
   // launched on the caller's own stream: no hand-over to a side stream and back.
@@ -188,6 +191,8 @@ class Engine {
     cudaEvent_t last_done = nullptr;
   };
   void launchLL(Channel& ch, const CollectiveDesc& d, cudaStream_t stream);
+  // 0: not for the flag-in-data kernels; 1: one-shot; 2: two-shot.
+  int llKind(const CollectiveDesc& d) const;
   void launch(Channel& ch, KernelId id, const OpArgs& a);
   void runAllreduceSlice(Channel& ch, const CollectiveDesc& d, const void* in, void* out,
                          int64_t n, Algo algo);

@@ -54,6 +54,7 @@ const char* kernelName(KernelId id) {
     case KernelId::P2P_DIRECT: return "direct_allreduce";
     case KernelId::NVLS_DIRECT: return "nvls_direct_allreduce";
     case KernelId::LL_ONESHOT: return "ll_allreduce";
+    case KernelId::LL_TWOSHOT: return "ll2_allreduce";
     case KernelId::PIPE: return "pipe_allreduce";
     default: return "?";
   }

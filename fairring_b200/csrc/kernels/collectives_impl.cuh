@@ -807,24 +807,23 @@ __device__ __forceinline__ void phaseDirectNvls(const ChannelDev& c, const OpArg
 // be at most one collective ahead of the slowest peer (it needs everybody's
 // words to finish), so the half written now was read two collectives ago.
 // ---------------------------------------------------------------------------
+// User-tensor access in 8-byte units and the spin on a flag-in-data word.
 template <typename T>
-__device__ __forceinline__ bool phaseLL(const ChannelDev& c, const OpArgs& a, const BlockCtx& bc) {
-  constexpr int E = 8 / sizeof(T);
+struct LLIo {
+  static constexpr int E = 8 / sizeof(T);
   using Acc = typename Tr<T>::Acc;
-  const Topo& t = c.topo;
-  const int W = t.world;
-  const int64_t n = a.seg.limit;
-  const int64_t units = ceilDiv(n, E);
-  const int64_t cap = (int64_t)(c.ll_half_bytes / 16 / kMaxRanks);  // units per source rank
-  const uint32_t tag = bc.seq + 1u == 0u ? 1u : bc.seq + 1u;
-  const uint64_t half = (bc.seq & 1u) ? c.ll_half_bytes : 0;
-  const T* in = static_cast<const T*>(a.in[blockIdx.y]);
-  T* out = static_cast<T*>(a.out[blockIdx.y]);
-  const bool in_al = (reinterpret_cast<uintptr_t>(in) & 7u) == 0;
-  const bool out_al = (reinterpret_cast<uintptr_t>(out) & 7u) == 0;
-  char* own = c.ll[t.rank] + half;
-
-  auto loadUnit = [&](int64_t u, Acc (&x)[E]) {
+  const T* in;
+  T* out;
+  int64_t n;
+  float scale;
+  bool in_al, out_al;
+  __device__ __forceinline__ LLIo(const void* i, void* o, int64_t n_, float s)
+      : in(static_cast<const T*>(i)), out(static_cast<T*>(o)), n(n_), scale(s),
+        in_al((reinterpret_cast<uintptr_t>(i) & 7u) == 0),
+        out_al((reinterpret_cast<uintptr_t>(o) & 7u) == 0) {}
+  // Unit u of the input, scaled, as it travels (rounded to T).
+  __device__ __forceinline__ uint2 load(int64_t u) const {
+    Acc x[E];
     const int64_t e0 = u * E;
     if (in_al && e0 + E <= n) {
       const uint2 raw = *reinterpret_cast<const uint2*>(in + e0);
@@ -835,74 +834,100 @@ __device__ __forceinline__ bool phaseLL(const ChannelDev& c, const OpArgs& a, co
 #pragma unroll
       for (int i = 0; i < E; ++i) x[i] = e0 + i < n ? Tr<T>::up(in[e0 + i]) : Acc(0);
     }
-    applyScale(x, a.scale);
-  };
-  auto packUnit = [&](const Acc (&x)[E]) {
+    applyScale(x, scale);
+    return pack(x);
+  }
+  static __device__ __forceinline__ uint2 pack(const Acc (&x)[E]) {
     uint2 raw;
     T* e = reinterpret_cast<T*>(&raw);
 #pragma unroll
     for (int i = 0; i < E; ++i) e[i] = Tr<T>::down(x[i]);
     return raw;
-  };
+  }
+  static __device__ __forceinline__ void unpack(const uint2& d, Acc (&x)[E]) {
+    const T* e = reinterpret_cast<const T*>(&d);
+#pragma unroll
+    for (int i = 0; i < E; ++i) x[i] = Tr<T>::up(e[i]);
+  }
+  __device__ __forceinline__ void store(int64_t u, const uint2& d) const {
+    const int64_t e0 = u * E;
+    if (out_al && e0 + E <= n) {
+      *reinterpret_cast<uint2*>(out + e0) = d;
+    } else {
+      const T* e = reinterpret_cast<const T*>(&d);
+#pragma unroll
+      for (int i = 0; i < E; ++i)
+        if (e0 + i < n) out[e0 + i] = e[i];
+    }
+  }
+};
+
+// Spins until the 16-byte word at p carries `tag` in both flag positions.
+// Bounded: on expiry records (timeout | aborted, peer q) and returns false.
+__device__ __forceinline__ bool llWait(const ChannelDev& c, const BlockCtx& bc, const char* p,
+                                       uint32_t tag, int q, uint2* data) {
+  uint4 w = ldStage(p);
+  if (w.y != tag || w.w != tag) {
+    uint64_t t0 = 0;
+    const uint64_t iter_cap = c.timeout_ns / 32 + (1ull << 20);
+    for (uint64_t it = 1;; ++it) {
+      w = ldStage(p);
+      if (w.y == tag && w.w == tag) break;
+      if ((it & 63) == 0) {
+        const uint64_t now = globalTimerNs();
+        if (t0 == 0) t0 = now;
+        const bool aborted =
+            (it & 1023) == 0 && c.abort_flag != nullptr && ldVolatile(c.abort_flag) != 0;
+        if (now - t0 > c.timeout_ns || it > iter_cap || aborted) {
+          volatile uint32_t* st = c.status;
+          st[1] = 0;
+          st[2] = (uint32_t)q;
+          st[3] = bc.seq;
+          __threadfence_system();
+          st[0] = aborted ? kStatusAborted : kStatusTimeout;
+          return false;
+        }
+      }
+    }
+  }
+  *data = make_uint2(w.x, w.z);
+  return true;
+}
+
+template <typename T>
+__device__ __forceinline__ bool phaseLL(const ChannelDev& c, const OpArgs& a, const BlockCtx& bc) {
+  constexpr int E = 8 / sizeof(T);
+  using Acc = typename Tr<T>::Acc;
+  const Topo& t = c.topo;
+  const int W = t.world;
+  const LLIo<T> io(a.in[blockIdx.y], a.out[blockIdx.y], a.seg.limit, a.scale);
+  const int64_t units = ceilDiv(io.n, E);
+  const int64_t cap = (int64_t)(c.ll_half_bytes / 16 / kMaxRanks);  // units per source rank
+  const uint32_t tag = bc.seq + 1u == 0u ? 1u : bc.seq + 1u;
+  const uint64_t half = (bc.seq & 1u) ? c.ll_half_bytes : 0;
+  char* own = c.ll[t.rank] + half;
 
   const int64_t stride = (int64_t)bc.G * kThreads;
   for (int64_t u = (int64_t)bc.b * kThreads + threadIdx.x; u < units; u += stride) {
-    Acc x[E];
-    loadUnit(u, x);
-    const uint2 d = packUnit(x);
+    const uint2 d = io.load(u);
     const uint4 word = make_uint4(d.x, tag, d.y, tag);
 #pragma unroll
     for (int k = 1; k < kMaxRanks; ++k)
       if (k < W)
         stStage(c.ll[(t.rank + k) % W] + half + ((int64_t)t.rank * cap + u) * 16, word);
   }
-  bool ok = true;
-  for (int64_t u = (int64_t)bc.b * kThreads + threadIdx.x; ok && u < units; u += stride) {
+  for (int64_t u = (int64_t)bc.b * kThreads + threadIdx.x; u < units; u += stride) {
     Acc acc[E];
 #pragma unroll
     for (int q = 0; q < kMaxRanks; ++q) {
       if (q >= W) break;
+      uint2 d;
+      if (q == t.rank)
+        d = io.load(u);  // what the peers got: the value after the round trip through T
+      else if (!llWait(c, bc, own + ((int64_t)q * cap + u) * 16, tag, q, &d))
+        return false;
       Acc x[E];
-      if (q == t.rank) {
-        loadUnit(u, x);
-        // what the peers got: the value after the round trip through T
-        const uint2 d = packUnit(x);
-        const T* e = reinterpret_cast<const T*>(&d);
-#pragma unroll
-        for (int i = 0; i < E; ++i) x[i] = Tr<T>::up(e[i]);
-      } else {
-        const char* p = own + ((int64_t)q * cap + u) * 16;
-        uint4 w = ldStage(p);
-        if (w.y != tag || w.w != tag) {
-          uint64_t t0 = 0;
-          const uint64_t iter_cap = c.timeout_ns / 32 + (1ull << 20);
-          for (uint64_t it = 1;; ++it) {
-            w = ldStage(p);
-            if (w.y == tag && w.w == tag) break;
-            if ((it & 63) == 0) {
-              const uint64_t now = globalTimerNs();
-              if (t0 == 0) t0 = now;
-              const bool aborted = (it & 1023) == 0 && c.abort_flag != nullptr &&
-                                   ldVolatile(c.abort_flag) != 0;
-              if (now - t0 > c.timeout_ns || it > iter_cap || aborted) {
-                volatile uint32_t* st = c.status;
-                st[1] = 0;
-                st[2] = (uint32_t)q;
-                st[3] = bc.seq;
-                __threadfence_system();
-                st[0] = aborted ? kStatusAborted : kStatusTimeout;
-                ok = false;
-                break;
-              }
-            }
-          }
-          if (!ok) break;
-        }
-        const uint2 d = make_uint2(w.x, w.z);
-        const T* e = reinterpret_cast<const T*>(&d);
-#pragma unroll
-        for (int i = 0; i < E; ++i) x[i] = Tr<T>::up(e[i]);
-      }
+      LLIo<T>::unpack(d, x);
       if (q == 0) {
 #pragma unroll
         for (int i = 0; i < E; ++i) acc[i] = x[i];
@@ -911,17 +936,91 @@ __device__ __forceinline__ bool phaseLL(const ChannelDev& c, const OpArgs& a, co
         for (int i = 0; i < E; ++i) acc[i] = combine(acc[i], x[i], a.op);
       }
     }
-    if (!ok) break;
-    const int64_t e0 = u * E;
-    if (out_al && e0 + E <= n) {
-      *reinterpret_cast<uint2*>(out + e0) = packUnit(acc);
-    } else {
-#pragma unroll
-      for (int i = 0; i < E; ++i)
-        if (e0 + i < n) out[e0 + i] = Tr<T>::down(acc[i]);
+    io.store(u, LLIo<T>::pack(acc));
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// Phase: flag-in-data two-shot (a few hundred KiB to a MiB or two).  Same words
+// as above, but the message is reduce-scattered and all-gathered: rank r
+// receives everybody's units of chunk r (area A: [source rank][unit]), reduces
+// them in rank order and sends the result to everybody (area B: [chunk][unit]).
+// Every unit crosses NVLink twice as 16 bytes instead of W times: for a 1 MiB
+// message 3.5 MiB leave each GPU, as for a 256 KiB one-shot.  Still no barrier.
+// A half of the area holds A and B: 2 x W x (units per chunk) words.
+// ---------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ bool phaseLL2(const ChannelDev& c, const OpArgs& a, const BlockCtx& bc) {
+  constexpr int E = 8 / sizeof(T);
+  using Acc = typename Tr<T>::Acc;
+  const Topo& t = c.topo;
+  const int W = t.world;
+  const LLIo<T> io(a.in[blockIdx.y], a.out[blockIdx.y], a.seg.limit, a.scale);
+  const int64_t units = ceilDiv(io.n, E);
+  const int64_t cu = ceilDiv(units, W);  // units per chunk
+  const uint32_t tag = bc.seq + 1u == 0u ? 1u : bc.seq + 1u;
+  const uint64_t half = (bc.seq & 1u) ? c.ll_half_bytes : 0;
+  const uint64_t areaB = (uint64_t)W * cu * 16;
+  const int64_t stride = (int64_t)bc.G * kThreads;
+  const int64_t first = (int64_t)bc.b * kThreads + threadIdx.x;
+
+  // 1. My units of every other rank's chunk go to that rank.
+  for (int k = 1; k < W; ++k) {
+    const int p = (t.rank + k) % W;
+    char* dst = c.ll[p] + half + (int64_t)t.rank * cu * 16;
+    for (int64_t u = first; u < cu; u += stride) {
+      const int64_t g = (int64_t)p * cu + u;
+      if (g >= units) break;
+      const uint2 d = io.load(g);
+      stStage(dst + u * 16, make_uint4(d.x, tag, d.y, tag));
     }
   }
-  return ok;
+  // 2. Reduce my chunk in rank order; the result goes to everybody.
+  char* ownA = c.ll[t.rank] + half;
+  for (int64_t u = first; u < cu; u += stride) {
+    const int64_t g = (int64_t)t.rank * cu + u;
+    if (g >= units) break;
+    Acc acc[E];
+#pragma unroll
+    for (int q = 0; q < kMaxRanks; ++q) {
+      if (q >= W) break;
+      uint2 d;
+      if (q == t.rank)
+        d = io.load(g);
+      else if (!llWait(c, bc, ownA + ((int64_t)q * cu + u) * 16, tag, q, &d))
+        return false;
+      Acc x[E];
+      LLIo<T>::unpack(d, x);
+      if (q == 0) {
+#pragma unroll
+        for (int i = 0; i < E; ++i) acc[i] = x[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < E; ++i) acc[i] = combine(acc[i], x[i], a.op);
+      }
+    }
+    const uint2 r = LLIo<T>::pack(acc);
+    const uint4 word = make_uint4(r.x, tag, r.y, tag);
+#pragma unroll
+    for (int k = 1; k < kMaxRanks; ++k)
+      if (k < W)
+        stStage(c.ll[(t.rank + k) % W] + half + areaB + ((int64_t)t.rank * cu + u) * 16, word);
+    io.store(g, r);
+  }
+  // 3. The other chunks, reduced by their owners.
+  char* ownB = c.ll[t.rank] + half + areaB;
+  for (int k = 1; k < W; ++k) {
+    const int p = (t.rank + k) % W;
+    for (int64_t u = first; u < cu; u += stride) {
+      const int64_t g = (int64_t)p * cu + u;
+      if (g >= units) break;
+      uint2 d;
+      if (!llWait(c, bc, ownB + ((int64_t)p * cu + u) * 16, tag, p, &d)) return false;
+      io.store(g, d);
+    }
+  }
+  return true;
 }
 
 // ---------------------------------------------------------------------------
@@ -980,6 +1079,8 @@ __device__ __forceinline__ void body(const ChannelDev& c, const OpArgs& a) {
     }
   } else if constexpr (K == KernelId::LL_ONESHOT) {
     phaseLL<WIRE>(c, a, bc);
+  } else if constexpr (K == KernelId::LL_TWOSHOT) {
+    phaseLL2<WIRE>(c, a, bc);
   }
   leave(c, a, bc);
 }
@@ -1006,6 +1107,7 @@ FR_DEFINE_KERNEL(nvls_oneshot_allreduce, KernelId::NVLS_ONESHOT)
 FR_DEFINE_KERNEL(direct_allreduce, KernelId::P2P_DIRECT)
 FR_DEFINE_KERNEL(nvls_direct_allreduce, KernelId::NVLS_DIRECT)
 FR_DEFINE_KERNEL(ll_allreduce, KernelId::LL_ONESHOT)
+FR_DEFINE_KERNEL(ll2_allreduce, KernelId::LL_TWOSHOT)
 
 
 using KernelFn = void (*)(const ChannelDev*, const OpArgs);
@@ -1037,6 +1139,9 @@ KernelFn kernelFor(KernelId id) {
       return nullptr;
     case KernelId::LL_ONESHOT:
       if constexpr (std::is_same<IO, WIRE>::value) return ll_allreduce<IO, WIRE>;
+      return nullptr;
+    case KernelId::LL_TWOSHOT:
+      if constexpr (std::is_same<IO, WIRE>::value) return ll2_allreduce<IO, WIRE>;
       return nullptr;
     default: return nullptr;
   }

@@ -73,6 +73,7 @@ enum class KernelId : int32_t {
   NVLS_DIRECT,          // in place on symmetric memory: multimem.ld_reduce + multimem.st
   LL_ONESHOT,           // small messages: every 16-byte store carries 8 bytes of data and two
                         // copies of the collective's number; receivers spin on the data itself
+  LL_TWOSHOT,           // the same words, reduce-scattered and all-gathered (mid-size messages)
   PIPE,                 // ordinary tensors: copy-in / reduce / copy-out pipelined over chunks
                         // (pipe_allreduce.h; counted here, launched through launchPipeAllreduce)
   kCount

@@ -18,7 +18,7 @@ using namespace dev;
 
 constexpr int kMaxStages = 8;
 constexpr int kNR = kPipeRedGroups;
-constexpr int kFirstRedWarp = 4;  // warps 0..3: copy-in, copy-out, publisher, spare
+constexpr int kFirstRedWarp = 2;  // warps 0, 1: copy-in, copy-out
 constexpr int kRedWarps = (kPipeThreads / 32 - kFirstRedWarp) / kNR;  // warps per reduce group
 constexpr int kRedThreads = kRedWarps * 32;
 
@@ -327,7 +327,7 @@ __device__ __forceinline__ void copyRole(const PipeChannelDev& c, const PipeArgs
   };
   auto waitReduced = [&](int k, bool block) -> int {  // copy-out: 1 ready, 0 not yet, -1 failed
     const uint32_t gg = g0 + (uint32_t)k;
-    const uint32_t* f = counterAt(my_pad, 1 + (int)(gg % kNR), lane < g.W ? lane : 0, g.b);
+    const uint32_t* f = counterAt(my_pad, kNR + (int)(gg % kNR), lane < g.W ? lane : 0, g.b);
     bool mine = true;
     if (block) {
       if (lane < g.W) mine = waitCounter(c, ctl, f, gg + 1u, kWaitReduce, (uint32_t)lane);
@@ -487,42 +487,6 @@ __device__ __forceinline__ void copyRole(const PipeChannelDev& c, const PipeArgs
   __syncwarp();
 }
 
-// ---- the publisher ------------------------------------------------------------
-// Waits for copy-in's word in shared memory, then makes the chunk visible to the
-// other GPUs (fence) and raises this block's copy-in counter on every rank.
-__device__ __forceinline__ void publishRole(const PipeChannelDev& c, const PipeArgs& a, const Geo& g,
-                                            Ctl* ctl, uint32_t g0) {
-  const int lane = threadIdx.x & 31;
-  for (int k = 0; k < g.nchunks; ++k) {
-    const uint32_t want = g0 + (uint32_t)k + 1u;
-    bool mine = true;
-    if (lane == 0) {
-      uint64_t t0 = 0;
-      for (uint64_t n = 1;; ++n) {
-        if ((int32_t)(ctl->cin_done - want) >= 0) break;
-        if ((n & 255) == 0) {
-          if (ctl->failed) {
-            mine = false;
-            break;
-          }
-          const uint64_t now = globalTimerNs();
-          if (t0 == 0) t0 = now;
-          if (now - t0 > 2 * c.timeout_ns || n > (1ull << 34)) {
-            recordFailure(c, ctl, kStatusTimeout, kWaitCopyInLocal, (uint32_t)c.rank, want - 1u);
-            mine = false;
-            break;
-          }
-        }
-      }
-    }
-    if (!__all_sync(0xffffffffu, mine)) return;
-    if (lane < g.W) {
-      __threadfence_system();
-      stReleaseSys(counterAt(c.flags[lane], 0, c.rank, g.b), want);
-    }
-  }
-}
-
 // ---- the reduce role ----------------------------------------------------------
 // Peer-load flavour: read the vector from every rank's ring, reduce in rank
 // order (the same bits on every GPU), write the result into every rank's ring.
@@ -626,8 +590,34 @@ __device__ __forceinline__ void reduceRole(const PipeChannelDev& c, const PipeAr
   for (; k < g.nchunks; k += kNR, slot = (slot + kNR) % g.slots) {
     const uint32_t gg = g0 + (uint32_t)k;
     bool bad = false;
-    if (gtid < g.W)
-      bad = !waitCounter(c, ctl, counterAt(my_pad, 0, gtid, g.b), gg + 1u, kWaitCopyIn, (uint32_t)gtid);
+    // 1. This block's copy-in of the chunk: wait for the copy warp's word, make
+    //    the chunk visible to the other GPUs, raise the counter everywhere.
+    if (gtid < g.W) {
+      uint64_t t0 = 0;
+      for (uint64_t n = 1;; ++n) {
+        if ((int32_t)(ctl->cin_done - (gg + 1u)) >= 0) break;
+        if ((n & 255) == 0) {
+          if (ctl->failed) {
+            bad = true;
+            break;
+          }
+          const uint64_t now = globalTimerNs();
+          if (t0 == 0) t0 = now;
+          if (now - t0 > 2 * c.timeout_ns || n > (1ull << 34)) {
+            recordFailure(c, ctl, kStatusTimeout, kWaitCopyInLocal, (uint32_t)c.rank, gg);
+            bad = true;
+            break;
+          }
+        }
+      }
+      if (!bad) {
+        __threadfence_system();
+        stReleaseSys(counterAt(c.flags[gtid], group, c.rank, g.b), gg + 1u);
+        // 2. Every rank's copy-in of the chunk.
+        bad = !waitCounter(c, ctl, counterAt(my_pad, group, gtid, g.b), gg + 1u, kWaitCopyIn,
+                           (uint32_t)gtid);
+      }
+    }
     if (namedBarrierOr(bar_id, kRedThreads, bad || ctl->failed != 0)) break;
     const int64_t c_lo = (int64_t)k * g.cv;
     const Piece p = pieceAt(g, c_lo, c.rank, g.b);  // whole vectors, the padded tail vector included
@@ -636,7 +626,7 @@ __device__ __forceinline__ void reduceRole(const PipeChannelDev& c, const PipeAr
     if (namedBarrierOr(bar_id, kRedThreads, ctl->failed != 0)) break;
     if (gtid < g.W) {
       __threadfence_system();
-      stReleaseSys(counterAt(c.flags[gtid], 1 + group, c.rank, g.b), gg + 1u);
+      stReleaseSys(counterAt(c.flags[gtid], kNR + group, c.rank, g.b), gg + 1u);
     }
   }
 }
@@ -679,9 +669,7 @@ pipe_allreduce(const PipeChannelDev* __restrict__ chs, const __grid_constant__ P
   } else if (warp == 1) {
     copyRole<false>(c, a, g, ctl, stages + (size_t)a.stages * a.stage_bytes, g0, nullptr,
                     static_cast<char*>(a.out[blockIdx.y]));
-  } else if (warp == 2) {
-    publishRole(c, a, g, ctl, g0);
-  } else if (warp >= kFirstRedWarp) {
+  } else {
     const int group = (warp - kFirstRedWarp) / kRedWarps;
     const int gtid = (int)threadIdx.x - (kFirstRedWarp + group * kRedWarps) * 32;
     reduceRole<T, NVLS>(c, a, g, ctl, g0, group, gtid);

@@ -7,12 +7,14 @@
 //   copy-in   one warp; bulk-copies (cp.async.bulk through shared memory, one
 //             elected thread) this block's pieces of chunk k from the user's
 //             tensor into this GPU's slot of a ring of symmetric staging memory
-//   publish   one warp; once copy-in says that a chunk's bulk stores are
-//             complete it fences and tells the peers -- the fence takes
-//             microseconds and must not stall the copy-in warp
-//   reduce    twelve warps in six groups that take chunks in turn, so that the
-//             latency of one chunk's switch round trip and of its fence is
-//             hidden behind five other chunks; rank r reduces
+//   reduce    fourteen warps in seven groups that take chunks in turn.  The
+//             group of chunk g first publishes this block's copy-in of g (it
+//             waits for copy-in's word in shared memory, fences, raises the
+//             counter on every rank), then waits for every rank's counter and
+//             reduces.  A system-scope fence on an SM that is streaming bulk
+//             stores takes some ten microseconds: it must stall neither the
+//             copy warps nor the other chunks, so every chunk's fences belong
+//             to its own group and seven chunks are in flight.  Rank r reduces
 //             sub-chunk r of the chunk over all GPUs and writes the result back
 //             into every GPU's ring slot (multimem.ld_reduce + multimem.st
 //             through the NVSwitch, or peer loads + peer stores)
@@ -23,6 +25,8 @@
 // of block b only ever wait for block b of the peers: per-(rank, block)
 // counters in symmetric memory, written with release stores after the data,
 // say "rank q, block b has copied in chunk g" and "... has reduced chunk g".
+// Each group has its own pair of counters (chunks of different groups may
+// finish out of order; a counter only ever grows).
 // Chunks are numbered across launches, a ring slot is reused every `slots`
 // chunks, and copy-in of chunk g waits for this block's copy-out of chunk
 // g - slots, which in turn has waited for every peer's reduce of that chunk:
@@ -41,10 +45,10 @@
 
 namespace fairring {
 
-constexpr int kPipeRedGroups = 6;                  // reduce groups (2 warps each) taking chunks in turn
-constexpr int kPipeLanes = 1 + kPipeRedGroups;     // counter lanes: copy-in, one per reduce group
+constexpr int kPipeRedGroups = 7;                  // reduce groups (2 warps each) taking chunks in turn
+constexpr int kPipeLanes = 2 * kPipeRedGroups;     // counters per (rank, block): copied-in and reduced, per group
 constexpr size_t kPipeFlagBytes = (size_t)kPipeLanes * kMaxRanks * kMaxBlocks * sizeof(uint32_t);
-constexpr int kPipeThreads = 512;                  // copy-in, copy-out, publisher, (spare), 6 x 2 reduce warps
+constexpr int kPipeThreads = 512;                  // copy-in warp, copy-out warp, 7 x 2 reduce warps
 
 // One channel as seen by one rank; lives in device memory.
 struct PipeChannelDev {

@@ -150,6 +150,8 @@ class FlatDataParallel(nn.Module):
         self._works = []
         self._callback_queued = False
         self._accumulate = False
+        self._overlap_tail = False
+        self._tail = None
         self.require_backward_grad_sync = True
         self._off_of = {id(p): off for p, off in zip(order, offsets)}
         for p in order:
@@ -225,6 +227,21 @@ class FlatDataParallel(nn.Module):
             elif strict:
                 raise KeyError(f"unexpected key in state_dict: {k}")
 
+    def enable_tail_overlap(self) -> None:
+        """Called by an optimizer that can start before the last bucket is
+        reduced (:class:`fairring_b200.ops.FlatAdamW` with ``overlap=``): the end
+        of backward then waits for every bucket but the last one, whose
+        parameters (the ones whose gradients arrive last) the optimizer updates
+        after waiting for it itself, see :meth:`take_tail`.  Code that reads
+        ``flat_grad`` right after backward must not enable this."""
+        self._overlap_tail = True
+
+    def take_tail(self):
+        """``(first element, [work, ...])`` of the bucket whose all-reduce may
+        still be running, or ``None``; the caller waits for the works."""
+        tail, self._tail = self._tail, None
+        return tail
+
     def no_sync(self):
         """Context manager: accumulate locally, skip the all-reduce (like DDP's)."""
         outer = self
@@ -291,7 +308,12 @@ class FlatDataParallel(nn.Module):
             while self._next_to_launch < len(self._buckets):  # parameters that got no gradient
                 self._launch(self._next_to_launch)
                 self._next_to_launch += 1
-            for w in self._works:
+            works = self._works
+            self._tail = None
+            if self._overlap_tail and len(works) >= 2 and len(works) == len(self._buckets):
+                self._tail = (self._buckets[-1][0], [works[-1]])
+                works = works[:-1]
+            for w in works:
                 w.wait()  # stream-level: the compute stream waits, the host does not
             self._accumulate = False
             # Host-side look at the kernels' status words (no synchronisation): a
