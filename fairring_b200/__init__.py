@@ -118,6 +118,7 @@ _TUNABLES = {
     "nvls_oneshot_max_bytes": "FAIRRING_NVLS_ONESHOT_MAX",
     "pipe_min_bytes": "FAIRRING_PIPE_MIN",
     "pipe_blocks": "FAIRRING_PIPE_BLOCKS",
+    "pipe_chunk_bytes": "FAIRRING_PIPE_CHUNK",
     "blocks": "FAIRRING_BLOCKS",
     "direct_max_slices": "FAIRRING_DIRECT_MAX_SLICES",
     "direct_unroll": "FAIRRING_DIRECT_UNROLL",

@@ -40,7 +40,7 @@ def main(argv=None) -> int:
     ap.add_argument("--what", default="direct,pipe,small,nccl")
     ap.add_argument("--dtype", default="fp32")
     ap.add_argument("--big-sizes", default="8388608,33554432,268435456")
-    ap.add_argument("--pipe-sizes", default="1048576,4194304,33554432,268435456")
+    ap.add_argument("--pipe-sizes", default="4194304,16777216,33554432,67108864,134217728,268435456")
     ap.add_argument("--iters", type=int, default=15)
     ap.add_argument("--json", default="", help="write all rows to this file")
     ap.add_argument("--write-table", action="store_true",
@@ -135,7 +135,7 @@ def main(argv=None) -> int:
         sym = be.symmetric_empty((512 << 20) // es, dtype)
         sym.normal_()
         setopt(direct_min_slice_bytes=1 << 20)
-        for blocks, slices, unroll in itertools.product((8, 16, 24, 32), (1, 2, 4), (4, 8, 16)):
+        for blocks, slices, unroll in itertools.product((4, 6, 8, 12, 16), (1, 2), (4, 8)):
             setopt(blocks=blocks, direct_max_slices=slices, direct_unroll=unroll)
             for size in big:
                 us, bw = measure(sym, size)
@@ -146,13 +146,13 @@ def main(argv=None) -> int:
 
     if "pipe" in what and world > 1:
         setopt(algo=ALGO["pipe"], ll_max_bytes=0)
-        for blocks, chunk in itertools.product((8, 16, 24, 32), (1 << 20, 2 << 20, 4 << 20, 8 << 20)):
+        for blocks, chunk in itertools.product((8, 16, 24, 32), (1 << 20, 2 << 20, 4 << 20)):
             setopt(pipe_blocks=blocks, pipe_chunk_bytes=chunk)
             for size in [int(x) for x in args.pipe_sizes.split(",")]:
                 us, bw = measure(arena, size)
                 add("pipe", {"blocks": blocks, "chunk": chunk}, size, us, bw)
             arena.normal_()
-        for stage, stages in ((8 << 10, 8), (32 << 10, 3), (24 << 10, 4)):
+        for stage, stages in ((32 << 10, 3),):
             setopt(pipe_blocks=16, pipe_chunk_bytes=2 << 20, pipe_stage_bytes=16, pipe_stages=2)
             setopt(pipe_stages=stages, pipe_stage_bytes=stage)
             for size in (33554432, 268435456):
@@ -229,8 +229,6 @@ def derive_table(rows, world):
     table["ll2_max_bytes"] = ll2_max
     table["oneshot_max_bytes"] = max(oneshot_max, ll_max)
     table["nvls_oneshot_max_bytes"] = max(nvls1_max, table["oneshot_max_bytes"])
-    if pipe_min:
-        table["pipe_min_bytes"] = pipe_min
     direct = [r for r in rows if r.get("part") == "direct" and r["bytes"] == 33554432]
     if direct:
         top = max(direct, key=lambda r: r["busbw"])
@@ -240,12 +238,28 @@ def derive_table(rows, world):
         table["blocks"] = pick["blocks"]
         table["direct_max_slices"] = pick["channels"]
         table["direct_unroll"] = pick["unroll"]
-    pipe = [r for r in rows if r.get("part") == "pipe" and r["bytes"] == 33554432 and "stage" not in r]
+    big = max([r["bytes"] for r in rows if r.get("part") == "pipe"], default=0)
+    pipe = [r for r in rows if r.get("part") == "pipe" and r["bytes"] == big and "stage" not in r]
     if pipe:
         top = max(pipe, key=lambda r: r["busbw"])
         ok = [r for r in pipe if r["busbw"] >= 0.97 * top["busbw"]]
         pick = min(ok, key=lambda r: (r["blocks"], -r["busbw"]))
         table["pipe_blocks"] = pick["blocks"]
+        table["pipe_chunk_bytes"] = pick["chunk"]
+        # from which size on does that configuration beat the staged kernels?
+        mine = {r["bytes"]: r["us"] for r in rows if r.get("part") == "pipe" and "stage" not in r
+                and r["blocks"] == pick["blocks"] and r["chunk"] == pick["chunk"]}
+        staged = {}
+        for r in rows:
+            if r.get("part") == "staged":
+                staged[r["bytes"]] = min(staged.get(r["bytes"], 1e30), r["us"])
+        wins = None
+        for size in sorted(mine, reverse=True):
+            if size in staged and mine[size] < staged[size]:
+                wins = size
+            else:
+                break
+        table["pipe_min_bytes"] = wins if wins is not None else 1 << 40
     return table
 
 
