@@ -33,6 +33,20 @@ cudaError_t launchSumSq(const float* x, int64_t n, float* out, int sm_count, cud
 // cudaMemcpyAsync when a pointer is not 16-byte aligned).
 cudaError_t launchCopy(void* dst, const void* src, size_t bytes, int blocks, cudaStream_t stream);
 
+// LayerNorm over the last dimension (`cols`, a multiple of 8, at most 8192) of a
+// [rows, cols] tensor; x / dx are fp32 or bf16, y / dy are fp32 or bf16, the
+// affine parameters and the saved per-row mean and 1/std are fp32.
+cudaError_t launchLayerNormForward(const void* x, bool x_bf16, const float* gamma, const float* beta,
+                                   void* y, bool y_bf16, float* mean, float* rstd, int64_t rows,
+                                   int cols, float eps, int sm_count, cudaStream_t stream);
+// `partial`: scratch of layerNormBackwardBlocks(rows, sm_count) x 2 x cols floats.
+int layerNormBackwardBlocks(int64_t rows, int sm_count);
+cudaError_t launchLayerNormBackward(const void* dy, bool y_bf16, const void* x, bool x_bf16,
+                                    const float* gamma, const float* mean, const float* rstd, void* dx,
+                                    float* partial, float* dgamma, float* dbeta, int64_t rows, int cols,
+                                    int sm_count, cudaStream_t stream);
+
 uint64_t localLaunchCountImpl();
+void noteLocalLaunch();
 
 }  // namespace fairring

@@ -201,5 +201,6 @@ cudaError_t launchCopy(void* dst, const void* src, size_t bytes, int blocks, cud
 }
 
 uint64_t localLaunchCountImpl() { return g_local_launches.load(std::memory_order_relaxed); }
+void noteLocalLaunch() { g_local_launches.fetch_add(1, std::memory_order_relaxed); }
 
 }  // namespace fairring

@@ -7,6 +7,7 @@
 #include <torch/extension.h>
 
 #include <cmath>
+#include <tuple>
 
 #include "kernels/local_kernels.h"
 
@@ -78,6 +79,57 @@ at::Tensor sumSq(at::Tensor x) {
   TORCH_CHECK(e == cudaSuccess, "sumsq launch failed: ", cudaGetErrorString(e));
   return out;
 }
+
+// y, mean, rstd = layer_norm(x); y in `out_dtype` (fp32 or bf16).
+std::tuple<at::Tensor, at::Tensor, at::Tensor> layerNormForward(at::Tensor x, at::Tensor gamma,
+                                                                at::Tensor beta, double eps,
+                                                                at::ScalarType out_dtype) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() >= 1, "x must be a contiguous CUDA tensor");
+  TORCH_CHECK(x.scalar_type() == at::kFloat || x.scalar_type() == at::kBFloat16, "x must be fp32 or bf16");
+  TORCH_CHECK(out_dtype == at::kFloat || out_dtype == at::kBFloat16, "output must be fp32 or bf16");
+  const int64_t cols = x.size(-1);
+  const int64_t rows = x.numel() / std::max<int64_t>(cols, 1);
+  TORCH_CHECK(gamma.is_cuda() && beta.is_cuda() && gamma.scalar_type() == at::kFloat &&
+                  beta.scalar_type() == at::kFloat && gamma.is_contiguous() && beta.is_contiguous() &&
+                  gamma.numel() == cols && beta.numel() == cols,
+              "weight and bias must be contiguous fp32 CUDA vectors of the row length");
+  TORCH_CHECK(cols % 8 == 0 && cols <= 8192, "row length must be a multiple of 8, at most 8192");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor y = at::empty(x.sizes(), x.options().dtype(out_dtype));
+  at::Tensor mean = at::empty({rows}, x.options().dtype(at::kFloat));
+  at::Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  cudaError_t e = launchLayerNormForward(
+      x.data_ptr(), x.scalar_type() == at::kBFloat16, gamma.data_ptr<float>(), beta.data_ptr<float>(),
+      y.data_ptr(), out_dtype == at::kBFloat16, mean.data_ptr<float>(), rstd.data_ptr<float>(), rows,
+      (int)cols, (float)eps, sms, c10::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "layer_norm forward launch failed: ", cudaGetErrorString(e));
+  return std::make_tuple(y, mean, rstd);
+}
+
+// dx, dgamma, dbeta
+std::tuple<at::Tensor, at::Tensor, at::Tensor> layerNormBackward(at::Tensor dy, at::Tensor x,
+                                                                 at::Tensor gamma, at::Tensor mean,
+                                                                 at::Tensor rstd) {
+  TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && x.is_contiguous() && dy.sizes() == x.sizes(),
+              "dy and x must be contiguous and equally shaped");
+  TORCH_CHECK(dy.scalar_type() == at::kFloat || dy.scalar_type() == at::kBFloat16, "dy must be fp32 or bf16");
+  const int64_t cols = x.size(-1);
+  const int64_t rows = x.numel() / std::max<int64_t>(cols, 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  at::Tensor dx = at::empty_like(x);
+  at::Tensor dgamma = at::empty({cols}, gamma.options());
+  at::Tensor dbeta = at::empty({cols}, gamma.options());
+  at::Tensor partial = at::empty({(int64_t)layerNormBackwardBlocks(rows, sms), 2, cols}, gamma.options());
+  cudaError_t e = launchLayerNormBackward(
+      dy.data_ptr(), dy.scalar_type() == at::kBFloat16, x.data_ptr(), x.scalar_type() == at::kBFloat16,
+      gamma.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), dx.data_ptr(),
+      partial.data_ptr<float>(), dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), rows, (int)cols, sms,
+      c10::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "layer_norm backward launch failed: ", cudaGetErrorString(e));
+  return std::make_tuple(dx, dgamma, dbeta);
+}
 }  // namespace
 
 uint64_t localLaunchCount() { return localLaunchCountImpl(); }
@@ -91,6 +143,10 @@ void bindLocalOps(pybind11::module_& m) {
   m.def("bf16_grad_to_f32_", &bf16GradToF32, py::arg("dst"), py::arg("src"),
         py::arg("accumulate") = false);
   m.def("sumsq", &sumSq, py::arg("x"));
+  m.def("layer_norm_fwd", &layerNormForward, py::arg("x"), py::arg("weight"), py::arg("bias"),
+        py::arg("eps"), py::arg("out_dtype"));
+  m.def("layer_norm_bwd", &layerNormBackward, py::arg("dy"), py::arg("x"), py::arg("weight"),
+        py::arg("mean"), py::arg("rstd"));
 }
 
 }  // namespace fairring

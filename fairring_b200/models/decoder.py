@@ -23,6 +23,7 @@ class DecoderConfig:
     d_ff: int = 8192
     vocab: int = 51200
     seq_len: int = 1024
+    fused_norm: bool = True  # one-kernel LayerNorm on the GPU (fairring_b200.ops.FusedLayerNorm)
 
     @staticmethod
     def flagship() -> "DecoderConfig":
@@ -34,14 +35,22 @@ class DecoderConfig:
         return DecoderConfig(n_layer=2, d_model=128, n_head=4, d_ff=512, vocab=1024, seq_len=64)
 
 
+def _layer_norm(cfg: DecoderConfig) -> nn.LayerNorm:
+    if cfg.fused_norm:
+        from ..ops import FusedLayerNorm  # same parameters and state dict as nn.LayerNorm
+
+        return FusedLayerNorm(cfg.d_model)
+    return nn.LayerNorm(cfg.d_model)
+
+
 class Block(nn.Module):
     def __init__(self, cfg: DecoderConfig):
         super().__init__()
         self.n_head = cfg.n_head
-        self.ln1 = nn.LayerNorm(cfg.d_model)
+        self.ln1 = _layer_norm(cfg)
         self.qkv = nn.Linear(cfg.d_model, 3 * cfg.d_model)
         self.proj = nn.Linear(cfg.d_model, cfg.d_model)
-        self.ln2 = nn.LayerNorm(cfg.d_model)
+        self.ln2 = _layer_norm(cfg)
         self.fc1 = nn.Linear(cfg.d_model, cfg.d_ff)
         self.fc2 = nn.Linear(cfg.d_ff, cfg.d_model)
 
@@ -63,7 +72,7 @@ class DecoderLM(nn.Module):
         self.tok = nn.Embedding(cfg.vocab, cfg.d_model)
         self.pos = nn.Embedding(cfg.seq_len, cfg.d_model)
         self.blocks = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layer))
-        self.ln_f = nn.LayerNorm(cfg.d_model)
+        self.ln_f = _layer_norm(cfg)
         self.apply(self._init)
         for blk in self.blocks:  # scaled init of the residual projections
             nn.init.normal_(blk.proj.weight, std=0.02 / math.sqrt(2 * cfg.n_layer))

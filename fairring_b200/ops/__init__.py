@@ -1,3 +1,4 @@
 """Fused single-GPU ops used by the training drivers."""
 
 from .optim import FlatAdamW  # noqa: F401
+from .layernorm import FusedLayerNorm, fused_layer_norm  # noqa: F401

@@ -1,0 +1,62 @@
+"""The fused single-GPU ops against plain PyTorch fp32 references."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _need_gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+
+
+@pytest.mark.parametrize("cols", [128, 2048, 4104, 8192])
+@pytest.mark.parametrize("x_dtype,y_dtype", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                             (torch.bfloat16, torch.bfloat16)])
+def test_fused_layer_norm_matches_fp32_reference(cols, x_dtype, y_dtype):
+    _need_gpu()
+    from fairring_b200.ops import fused_layer_norm
+
+    torch.manual_seed(cols)
+    rows = 777
+    x = (torch.randn(rows, cols, device="cuda") * 2 + 0.5).to(x_dtype)
+    w = torch.randn(cols, device="cuda")
+    b = torch.randn(cols, device="cuda")
+    dy = torch.randn(rows, cols, device="cuda").to(y_dtype)
+
+    xr = x.float().clone().requires_grad_(True)
+    wr, br = w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    yr = torch.nn.functional.layer_norm(xr, (cols,), wr, br, 1e-5)
+    yr.backward(dy.float())
+
+    xf = x.clone().requires_grad_(True)
+    wf, bf = w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    yf = fused_layer_norm(xf, wf, bf, 1e-5, out_dtype=y_dtype)
+    assert yf.dtype == y_dtype
+    yf.backward(dy)
+    lo = y_dtype == torch.bfloat16 or x_dtype == torch.bfloat16
+    torch.testing.assert_close(yf.float(), yr, rtol=2e-2 if lo else 1e-5, atol=3e-2 if lo else 1e-5)
+    torch.testing.assert_close(xf.grad.float(), xr.grad, rtol=2e-2 if lo else 1e-4, atol=3e-2 if lo else 1e-5)
+    torch.testing.assert_close(wf.grad, wr.grad, rtol=1e-3, atol=0.3 if lo else 1e-3)
+    torch.testing.assert_close(bf.grad, br.grad, rtol=1e-3, atol=0.3 if lo else 1e-3)
+
+
+def test_fused_layer_norm_module_under_autocast_and_fallback():
+    _need_gpu()
+    from fairring_b200.ops import FusedLayerNorm
+
+    ln = FusedLayerNorm(256).cuda()
+    ref = torch.nn.LayerNorm(256).cuda()
+    ref.load_state_dict(ln.state_dict())
+    x = torch.randn(4, 33, 256, device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = ln(x)
+    assert y.dtype == torch.bfloat16
+    torch.testing.assert_close(y.float(), ref(x), rtol=2e-2, atol=3e-2)
+    assert ln(x).dtype == torch.float32
+    # a row length the kernel does not take: plain torch path
+    odd = FusedLayerNorm(100).cuda()
+    assert odd(torch.randn(3, 100, device="cuda")).shape == (3, 100)
+    # CPU: plain torch path
+    assert FusedLayerNorm(16)(torch.randn(2, 16)).shape == (2, 16)
