@@ -44,6 +44,7 @@ SOURCES = [
     "kernels/collectives_f32_f16.cu",
     "kernels/local_ops.cu",
     "kernels/layernorm.cu",
+    "kernels/cross_entropy.cu",
     "kernels/noalloc_allreduce.cu",
     "kernels/pipe_allreduce.cu",
 ]

@@ -46,6 +46,16 @@ cudaError_t launchLayerNormBackward(const void* dy, bool y_bf16, const void* x, 
                                     float* partial, float* dgamma, float* dbeta, int64_t rows, int cols,
                                     int sm_count, cudaStream_t stream);
 
+// Softmax cross-entropy over [rows, vocab] logits (fp32 or bf16, vocab a
+// multiple of 8): per-row loss and log-sum-exp; the backward overwrites the
+// logits with their gradient, scaled by *upstream (a device scalar) * scale.
+cudaError_t launchCrossEntropyForward(const void* logits, bool bf16, const int64_t* targets, float* loss,
+                                      float* lse, int64_t rows, int vocab, int sm_count,
+                                      cudaStream_t stream);
+cudaError_t launchCrossEntropyBackward(void* logits, bool bf16, const int64_t* targets, const float* lse,
+                                       const float* upstream, float scale, int64_t rows, int vocab,
+                                       int sm_count, cudaStream_t stream);
+
 uint64_t localLaunchCountImpl();
 void noteLocalLaunch();
 

@@ -130,6 +130,42 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> layerNormBackward(at::Tensor dy, 
   TORCH_CHECK(e == cudaSuccess, "layer_norm backward launch failed: ", cudaGetErrorString(e));
   return std::make_tuple(dx, dgamma, dbeta);
 }
+
+// (per-row loss, per-row log-sum-exp) of logits [rows, vocab] against targets [rows].
+std::tuple<at::Tensor, at::Tensor> crossEntropyForward(at::Tensor logits, at::Tensor targets) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous(),
+              "logits must be a contiguous 2-D CUDA tensor");
+  TORCH_CHECK(logits.scalar_type() == at::kFloat || logits.scalar_type() == at::kBFloat16,
+              "logits must be fp32 or bf16");
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous() &&
+                  targets.numel() == logits.size(0),
+              "targets must be a contiguous int64 CUDA vector with one entry per row");
+  TORCH_CHECK(logits.size(1) % 8 == 0, "the vocabulary size must be a multiple of 8");
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto fopt = logits.options().dtype(at::kFloat);
+  at::Tensor loss = at::empty({logits.size(0)}, fopt), lse = at::empty({logits.size(0)}, fopt);
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  cudaError_t e = launchCrossEntropyForward(logits.data_ptr(), logits.scalar_type() == at::kBFloat16,
+                                            targets.data_ptr<int64_t>(), loss.data_ptr<float>(),
+                                            lse.data_ptr<float>(), logits.size(0), (int)logits.size(1), sms,
+                                            c10::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "cross_entropy forward launch failed: ", cudaGetErrorString(e));
+  return std::make_tuple(loss, lse);
+}
+
+// Overwrites logits with d(loss)/d(logits) * upstream * scale.
+void crossEntropyBackward(at::Tensor logits, at::Tensor targets, at::Tensor lse, at::Tensor upstream,
+                          double scale) {
+  TORCH_CHECK(upstream.is_cuda() && upstream.scalar_type() == at::kFloat && upstream.numel() == 1,
+              "upstream must be a one-element fp32 CUDA tensor");
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  cudaError_t e = launchCrossEntropyBackward(
+      logits.data_ptr(), logits.scalar_type() == at::kBFloat16, targets.data_ptr<int64_t>(),
+      lse.data_ptr<float>(), upstream.data_ptr<float>(), (float)scale, logits.size(0), (int)logits.size(1),
+      sms, c10::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "cross_entropy backward launch failed: ", cudaGetErrorString(e));
+}
 }  // namespace
 
 uint64_t localLaunchCount() { return localLaunchCountImpl(); }
@@ -143,6 +179,9 @@ void bindLocalOps(pybind11::module_& m) {
   m.def("bf16_grad_to_f32_", &bf16GradToF32, py::arg("dst"), py::arg("src"),
         py::arg("accumulate") = false);
   m.def("sumsq", &sumSq, py::arg("x"));
+  m.def("cross_entropy_fwd", &crossEntropyForward, py::arg("logits"), py::arg("targets"));
+  m.def("cross_entropy_bwd_", &crossEntropyBackward, py::arg("logits"), py::arg("targets"),
+        py::arg("lse"), py::arg("upstream"), py::arg("scale"));
   m.def("layer_norm_fwd", &layerNormForward, py::arg("x"), py::arg("weight"), py::arg("bias"),
         py::arg("eps"), py::arg("out_dtype"));
   m.def("layer_norm_bwd", &layerNormBackward, py::arg("dy"), py::arg("x"), py::arg("weight"),

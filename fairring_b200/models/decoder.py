@@ -24,6 +24,7 @@ class DecoderConfig:
     vocab: int = 51200
     seq_len: int = 1024
     fused_norm: bool = True  # one-kernel LayerNorm on the GPU (fairring_b200.ops.FusedLayerNorm)
+    fused_loss: bool = True  # two-kernel cross-entropy on the GPU (fairring_b200.ops.fused_cross_entropy)
 
     @staticmethod
     def flagship() -> "DecoderConfig":
@@ -99,4 +100,8 @@ class DecoderLM(nn.Module):
         logits = F.linear(x, self.tok.weight)  # tied output embedding
         if targets is None:
             return logits
+        if self.cfg.fused_loss and logits.is_cuda:
+            from ..ops import fused_cross_entropy  # the logits are consumed: nothing else reads them
+
+            return fused_cross_entropy(logits.view(b * s, -1), targets.reshape(-1))
         return F.cross_entropy(logits.view(b * s, -1).float(), targets.reshape(-1))

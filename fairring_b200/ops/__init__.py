@@ -2,3 +2,4 @@
 
 from .optim import FlatAdamW  # noqa: F401
 from .layernorm import FusedLayerNorm, fused_layer_norm  # noqa: F401
+from .cross_entropy import fused_cross_entropy  # noqa: F401

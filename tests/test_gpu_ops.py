@@ -60,3 +60,30 @@ def test_fused_layer_norm_module_under_autocast_and_fallback():
     assert odd(torch.randn(3, 100, device="cuda")).shape == (3, 100)
     # CPU: plain torch path
     assert FusedLayerNorm(16)(torch.randn(2, 16)).shape == (2, 16)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("vocab", [1024, 51200])
+def test_fused_cross_entropy_matches_fp32_reference(dtype, vocab):
+    _need_gpu()
+    from fairring_b200.ops import fused_cross_entropy
+
+    torch.manual_seed(vocab)
+    rows = 300
+    base = (torch.randn(rows, vocab, device="cuda") * 3).to(dtype)
+    targets = torch.randint(0, vocab, (rows,), device="cuda")
+    targets[5] = -100  # ignored row
+
+    ref_in = base.float().clone().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(ref_in, targets, ignore_index=-100)
+    (ref * 1.7).backward()
+
+    # the logits must come out of an op (the loss overwrites them with their gradient)
+    leaf = base.clone().requires_grad_(True)
+    logits = leaf * 1.0
+    loss = fused_cross_entropy(logits, targets)
+    (loss * 1.7).backward()
+    lo = dtype == torch.bfloat16
+    torch.testing.assert_close(loss.float(), ref, rtol=1e-3 if lo else 1e-5, atol=1e-3 if lo else 1e-5)
+    torch.testing.assert_close(leaf.grad.float(), ref_in.grad, rtol=2e-2 if lo else 1e-4, atol=1e-4 if lo else 1e-7)
+    assert float(leaf.grad[5].abs().sum()) == 0.0
