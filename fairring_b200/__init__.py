@@ -35,6 +35,7 @@ FAIRRING_LL2_MAX               largest message (bytes) for its two-shot form (de
 FAIRRING_INLINE_SMALL          1 (default): a blocking all_reduce that fits that kernel runs on the
                                caller's own stream
 FAIRRING_ONESHOT_MAX           largest message (bytes) for the one-shot kernel
+FAIRRING_DIRECT_BLOCKS         thread blocks of an in-place launch on symmetric memory (0: FAIRRING_BLOCKS)
 FAIRRING_DIRECT_UNROLL         16-byte multimem loads a thread keeps in flight in the in-place kernel
 FAIRRING_NVLS                  auto | on | off   (NVSwitch multicast kernels)
 FAIRRING_NVLS_MIN              smallest message (bytes) for the NVLS two-shot kernel
@@ -122,6 +123,7 @@ _TUNABLES = {
     "blocks": "FAIRRING_BLOCKS",
     "direct_max_slices": "FAIRRING_DIRECT_MAX_SLICES",
     "direct_unroll": "FAIRRING_DIRECT_UNROLL",
+    "direct_blocks": "FAIRRING_DIRECT_BLOCKS",
 }
 
 
@@ -175,6 +177,7 @@ def options_from_env(timeout: timedelta | None = None, world: int = 0) -> "_C.Op
     opts.ll_channels = _env_int("FAIRRING_LL_CHANNELS", opts.ll_channels)
     opts.inline_small = os.environ.get("FAIRRING_INLINE_SMALL", "1") == "1"
     opts.direct_unroll = _env_int("FAIRRING_DIRECT_UNROLL", opts.direct_unroll)
+    opts.direct_blocks = _env_int("FAIRRING_DIRECT_BLOCKS", opts.direct_blocks)
     opts.nvls_min_bytes = _env_int("FAIRRING_NVLS_MIN", opts.nvls_min_bytes)
     opts.nvls_oneshot_max_bytes = _env_int("FAIRRING_NVLS_ONESHOT_MAX", opts.nvls_oneshot_max_bytes)
     opts.device_timeout_ms = _env_int("FAIRRING_DEVICE_TIMEOUT_MS", opts.device_timeout_ms)

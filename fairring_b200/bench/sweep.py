@@ -15,6 +15,8 @@ powers of two.  Every time is measured on the device with CUDA events around a
 train of back-to-back calls, each on a different slice of an arena larger than
 L2, and is the maximum over ranks.  busbw = 2 (W-1)/W * bytes / time.
 The grouping (1x8, 2x4, 4x2) comes from FAIRRING_GPUS_PER_MACHINE as usual.
+FAIRRING_TOTAL_MEMORY defaults to 512 MiB here (the engine's line in the JSON
+says what it made of it).
 """
 
 from __future__ import annotations
@@ -51,6 +53,9 @@ def main(argv=None) -> int:
     ap.add_argument("--json", default="", help="also write the rows to this file")
     args = ap.parse_args(argv)
 
+    # Staging for ordinary tensors: the library's default budget (50 MiB, the
+    # reference's) is sized for small GPUs; the sweep gives it 512 MiB of the 180 GB.
+    os.environ.setdefault("FAIRRING_TOTAL_MEMORY", str(512 << 20))
     import fairring_b200  # registers the backend
 
     rank = int(os.environ.get("RANK", "0"))

@@ -41,19 +41,24 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", default="fp32")
     ap.add_argument("--big-sizes", default="8388608,33554432,268435456")
     ap.add_argument("--pipe-sizes", default="4194304,16777216,33554432,67108864,134217728,268435456")
+    ap.add_argument("--pipe-blocks", default="8,16,32")
+    ap.add_argument("--pipe-chunks", default="1048576,4194304,16777216")
     ap.add_argument("--iters", type=int, default=15)
     ap.add_argument("--json", default="", help="write all rows to this file")
+    ap.add_argument("--merge", default="", help="a --json file of an earlier run: its rows stand in for "
+                    "the parts that this run does not measure")
     ap.add_argument("--write-table", action="store_true",
                     help="write fairring_b200/tuning.json from what was measured")
     args = ap.parse_args(argv)
     what = set(args.what.split(","))
 
-    os.environ.setdefault("FAIRRING_TOTAL_MEMORY", str(512 << 20))
+    os.environ.setdefault("FAIRRING_TOTAL_MEMORY", str(1 << 30))
     os.environ.setdefault("FAIRRING_SM_BUDGET", "148")
     os.environ.setdefault("FAIRRING_PARALLELISM", "4")
     os.environ.setdefault("FAIRRING_LL_MAX", str(256 << 10))
     os.environ.setdefault("FAIRRING_LL2_MAX", str(4 << 20))
-    os.environ.setdefault("FAIRRING_PIPE_SLOTS", "8")
+    os.environ.setdefault("FAIRRING_PIPE_SLOTS", "4")
+    os.environ.setdefault("FAIRRING_PIPE_CHANNELS", "1")
     os.environ["FAIRRING_TUNING_TABLE"] = "off"
     import fairring_b200
 
@@ -136,17 +141,18 @@ def main(argv=None) -> int:
         sym.normal_()
         setopt(direct_min_slice_bytes=1 << 20)
         for blocks, slices, unroll in itertools.product((4, 6, 8, 12, 16), (1, 2), (4, 8)):
-            setopt(blocks=blocks, direct_max_slices=slices, direct_unroll=unroll)
+            setopt(direct_blocks=blocks, direct_max_slices=slices, direct_unroll=unroll)
             for size in big:
                 us, bw = measure(sym, size)
                 add("direct", {"blocks": blocks, "channels": slices, "unroll": unroll}, size, us, bw)
             sym.normal_()
-        setopt(blocks=16, direct_max_slices=2, direct_unroll=8, direct_min_slice_bytes=2 << 20)
+        setopt(direct_blocks=0, direct_max_slices=2, direct_unroll=8, direct_min_slice_bytes=2 << 20)
         be.check_health()
 
     if "pipe" in what and world > 1:
         setopt(algo=ALGO["pipe"], ll_max_bytes=0)
-        for blocks, chunk in itertools.product((8, 16, 24, 32), (1 << 20, 2 << 20, 4 << 20)):
+        for blocks, chunk in itertools.product([int(x) for x in args.pipe_blocks.split(",")],
+                                               [int(x) for x in args.pipe_chunks.split(",")]):
             setopt(pipe_blocks=blocks, pipe_chunk_bytes=chunk)
             for size in [int(x) for x in args.pipe_sizes.split(",")]:
                 us, bw = measure(arena, size)
@@ -191,6 +197,11 @@ def main(argv=None) -> int:
         be.check_health()
 
     if rank == 0:
+        if args.merge and os.path.exists(args.merge):
+            with open(args.merge) as f:
+                earlier = json.load(f)["rows"]
+            mine = {r.get("part") for r in rows}
+            rows = [r for r in earlier if r.get("part") not in mine] + rows
         if args.json:
             with open(args.json, "w") as f:
                 json.dump({"describe": be.describe(), "world": world, "dtype": args.dtype, "rows": rows}, f, indent=1)
@@ -235,7 +246,7 @@ def derive_table(rows, world):
         # the smallest footprint within 3 % of the best
         ok = [r for r in direct if r["busbw"] >= 0.97 * top["busbw"]]
         pick = min(ok, key=lambda r: (r["blocks"] * r["channels"], -r["busbw"]))
-        table["blocks"] = pick["blocks"]
+        table["direct_blocks"] = pick["blocks"]
         table["direct_max_slices"] = pick["channels"]
         table["direct_unroll"] = pick["unroll"]
     big = max([r["bytes"] for r in rows if r.get("part") == "pipe"], default=0)

@@ -329,6 +329,7 @@ EngineConfig BackendFairring::engineConfig() const {
   cfg.ll2_max_bytes = options_->ll2_max_bytes;
   cfg.ll_channels = (int32_t)options_->ll_channels;
   cfg.inline_small = options_->inline_small;
+  cfg.direct_blocks = (int32_t)options_->direct_blocks;
   cfg.direct_unroll = (int32_t)options_->direct_unroll;
   cfg.nvls_min_bytes = options_->nvls_min_bytes;
   cfg.nvls_oneshot_max_bytes = options_->nvls_oneshot_max_bytes;

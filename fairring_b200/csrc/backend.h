@@ -52,6 +52,7 @@ struct OptionsFairring : c10d::Backend::Options {
   int64_t ll2_max_bytes = 1 << 20;   // ... and its two-shot form up to this size; 0: off
   int64_t ll_channels = 4;
   bool inline_small = true;          // blocking small all_reduce runs on the caller's stream
+  int64_t direct_blocks = 0;
   int64_t direct_unroll = 8;
   int64_t nvls_min_bytes = 0;
   int64_t nvls_oneshot_max_bytes = 2 << 20;

@@ -75,6 +75,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("ll2_max_bytes", &OptionsFairring::ll2_max_bytes)
       .def_readwrite("ll_channels", &OptionsFairring::ll_channels)
       .def_readwrite("inline_small", &OptionsFairring::inline_small)
+      .def_readwrite("direct_blocks", &OptionsFairring::direct_blocks)
       .def_readwrite("direct_unroll", &OptionsFairring::direct_unroll)
       .def_readwrite("nvls_min_bytes", &OptionsFairring::nvls_min_bytes)
       .def_readwrite("nvls_oneshot_max_bytes", &OptionsFairring::nvls_oneshot_max_bytes)

@@ -55,6 +55,8 @@ struct EngineConfig {
   // A blocking all_reduce (async_op=False) that fits the flag-in-data kernel is
   // launched on the caller's own stream: no hand-over to a side stream and back.
   bool inline_small = true;
+  int32_t direct_blocks = 0;           // blocks of an in-place launch (0: `blocks`); the switch
+                                       // saturates with few, and backward keeps the other SMs
   int32_t direct_unroll = 8;           // in-place NVLS kernel: 16-byte loads in flight per thread
   int64_t nvls_min_bytes = 0;          // below this the peer-load two-shot is used
   int64_t nvls_oneshot_max_bytes = 2 << 20;
@@ -193,7 +195,8 @@ class Engine {
   void launchLL(Channel& ch, const CollectiveDesc& d, cudaStream_t stream);
   // 0: not for the flag-in-data kernels; 1: one-shot; 2: two-shot.
   int llKind(const CollectiveDesc& d) const;
-  void launch(Channel& ch, KernelId id, const OpArgs& a);
+  void launch(Channel& ch, KernelId id, const OpArgs& a, int blocks = 0);
+  bool directEligible(const CollectiveDesc& d) const;
   void runAllreduceSlice(Channel& ch, const CollectiveDesc& d, const void* in, void* out,
                          int64_t n, Algo algo);
   bool findSymmetric(const void* p, size_t bytes, const SymmRegion** reg, size_t* off) const;
@@ -238,7 +241,7 @@ class Engine {
   std::vector<cudaEvent_t> free_events_;  // created on demand, reused after releaseEvent()
   std::mutex events_mu_;
   uint64_t next_channel_ = 0;
-  std::mutex mu_;
+  mutable std::mutex mu_;
   EngineStats stats_;
   std::vector<TraceEntry> trace_;  // ring of kTraceLen entries
   TraceEntry cur_;

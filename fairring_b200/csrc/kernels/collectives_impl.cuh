@@ -52,14 +52,23 @@ __device__ __forceinline__ bool barrier(const ChannelDev& c, const BlockCtx& bc,
   const uint32_t epoch = bc.seq * (uint32_t)kBarriersPerOp + (uint32_t)idx + 1u;
   const int n = KIND == kAll ? t.world : (KIND == kGroup ? t.D : t.M);
   __syncthreads();
+  // Arrive: ONE system-scope fence for the whole block (its writes reached
+  // thread 0 through the __syncthreads above), then a relaxed store per peer
+  // by that same thread.  A fence and a release-store in each of n threads is
+  // 2n system-scope membars that an SM works off one after the other.
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int i = 0; i < n; ++i) {
+      const int q = KIND == kAll ? i : (KIND == kGroup ? rankOf(t, t.m, i) : rankOf(t, i, t.d));
+      if (q != t.rank) stRelaxedSys(c.flags[q] + t.rank * kMaxBlocks + bc.b, epoch);
+    }
+  }
   uint32_t st = kStatusOk;
   int peer = -1;
   if ((int)threadIdx.x < n) {
     const int i = threadIdx.x;
     peer = KIND == kAll ? i : (KIND == kGroup ? rankOf(t, t.m, i) : rankOf(t, i, t.d));
     if (peer != t.rank) {
-      __threadfence_system();
-      stReleaseSys(c.flags[peer] + t.rank * kMaxBlocks + bc.b, epoch);
       st = waitFlag(c.flags[t.rank] + peer * kMaxBlocks + bc.b, epoch, c.timeout_ns,
                     c.abort_flag);
       if (st != kStatusOk) {
@@ -86,7 +95,14 @@ __device__ __forceinline__ BlockCtx enter(const ChannelDev& c) {
 
 __device__ __forceinline__ void leave(const ChannelDev& c, const OpArgs& a, const BlockCtx& bc) {
   __syncthreads();
-  if ((a.flags & kAdvanceSeq) && threadIdx.x == 0) c.seq[bc.b] = bc.seq + 1u;
+  if (a.flags & kAdvanceSeq) {
+    if (threadIdx.x == 0) c.seq[bc.b] = bc.seq + 1u;
+    // A launch narrower than the channel's grid: block 0 keeps the counts of the
+    // blocks that did not run in step (all counts of a channel are equal between
+    // kernels, and nothing else runs on the channel's stream meanwhile).
+    if (bc.b == 0)
+      for (int b = bc.G + (int)threadIdx.x; b < a.full_blocks; b += (int)blockDim.x) c.seq[b] = bc.seq + 1u;
+  }
 }
 
 __device__ __forceinline__ char* stageAt(char* slot, uint64_t half, int64_t vec) {

@@ -58,6 +58,8 @@ struct OpArgs {
   int32_t wire_dtype;  // DType held in staging and sent over NVLink
   uint32_t flags;      // OpFlags
   int32_t unroll;      // in-place NVLS kernel: 16-byte accesses in flight per thread (4, 8, 16)
+  int32_t full_blocks;  // blocks of the channel's widest launch; a narrower launch advances the
+                        // collective counts of the blocks that it does not run (0: none to advance)
 };
 
 enum class KernelId : int32_t {

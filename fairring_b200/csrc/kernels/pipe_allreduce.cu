@@ -592,7 +592,7 @@ __device__ __forceinline__ void reduceRole(const PipeChannelDev& c, const PipeAr
     bool bad = false;
     // 1. This block's copy-in of the chunk: wait for the copy warp's word, make
     //    the chunk visible to the other GPUs, raise the counter everywhere.
-    if (gtid < g.W) {
+    if (gtid == 0) {
       uint64_t t0 = 0;
       for (uint64_t n = 1;; ++n) {
         if ((int32_t)(ctl->cin_done - (gg + 1u)) >= 0) break;
@@ -611,12 +611,18 @@ __device__ __forceinline__ void reduceRole(const PipeChannelDev& c, const PipeAr
         }
       }
       if (!bad) {
+        // One system-scope fence, then a relaxed store per rank by the same
+        // thread: an SM works its system-scope membars off one after the other.
         __threadfence_system();
-        stReleaseSys(counterAt(c.flags[gtid], group, c.rank, g.b), gg + 1u);
-        // 2. Every rank's copy-in of the chunk.
+        for (int q = 0; q < g.W; ++q) stRelaxedSys(counterAt(c.flags[q], group, c.rank, g.b), gg + 1u);
+      }
+    }
+    // 2. Every rank's copy-in of the chunk.
+    if (gtid < 32) {
+      bad = __shfl_sync(0xffffffffu, (int)bad, 0) != 0;
+      if (!bad && gtid < g.W)
         bad = !waitCounter(c, ctl, counterAt(my_pad, group, gtid, g.b), gg + 1u, kWaitCopyIn,
                            (uint32_t)gtid);
-      }
     }
     if (namedBarrierOr(bar_id, kRedThreads, bad || ctl->failed != 0)) break;
     const int64_t c_lo = (int64_t)k * g.cv;
@@ -624,9 +630,10 @@ __device__ __forceinline__ void reduceRole(const PipeChannelDev& c, const PipeAr
     if (p.hi > p.lo)
       reducePiece<T, NVLS>(c, a, slotOffset(c, slot), p.lo - c_lo, p.hi - p.lo, gtid);
     if (namedBarrierOr(bar_id, kRedThreads, ctl->failed != 0)) break;
-    if (gtid < g.W) {
+    if (gtid == 0) {
       __threadfence_system();
-      stReleaseSys(counterAt(c.flags[gtid], kNR + group, c.rank, g.b), gg + 1u);
+      for (int q = 0; q < g.W; ++q)
+        stRelaxedSys(counterAt(c.flags[q], kNR + group, c.rank, g.b), gg + 1u);
     }
   }
 }

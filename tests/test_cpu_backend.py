@@ -295,14 +295,17 @@ def test_options_from_env(monkeypatch):
 
 
 # --- the process group can be torn down and built again in the same processes ----------
-def _w_reinit(rank, world):
+def _w_reinit(rank, world, folder):
     import torch.distributed as dist
 
     import fairring  # noqa: F401
 
     out = []
     for generation in range(3):
-        dist.init_process_group("fairring", rank=rank, world_size=world)
+        # A rendezvous file per generation: with one TCP port for all of them a fast
+        # rank can reach the slow rank's store of the generation before, which then goes away.
+        dist.init_process_group("fairring", rank=rank, world_size=world,
+                                init_method=f"file://{folder}/generation{generation}")
         t = torch.full((50_000,), float(rank + generation))
         dist.all_reduce(t)
         out.append(float(t[0]))
@@ -311,7 +314,7 @@ def _w_reinit(rank, world):
     return out
 
 
-def test_process_group_can_be_rebuilt():
-    res = run_ranks(_w_reinit, 2)
+def test_process_group_can_be_rebuilt(tmp_path):
+    res = run_ranks(_w_reinit, 2, args=(str(tmp_path),))
     for r in res:
         assert r == [1.0, 3.0, 5.0]

@@ -209,6 +209,8 @@ CONFIGS = {
     "pipe": {"FAIRRING_ALGO": "pipe", "FAIRRING_DIRECT": "nvls"},
     "pipe_p2p": {"FAIRRING_ALGO": "pipe", "FAIRRING_NVLS": "off"},
     "pipe_off": {"FAIRRING_PIPE": "off"},
+    # in-place launches of 4 blocks between staged and flag-in-data launches of 16
+    "narrow_in_place": {"FAIRRING_DIRECT": "nvls", "FAIRRING_DIRECT_BLOCKS": "4", "FAIRRING_PIPE": "off"},
     "hier_three_kernels": {"FAIRRING_ALGO": "hier", "FAIRRING_NVLS": "off"},
     "ipc_transport_cmd_thread": {"FAIRRING_TRANSPORT": "ipc", "FAIRRING_COMMAND_THREAD": "1"},
     "machines_of_one_gpu": {"FAIRRING_GPUS_PER_MACHINE": "1", "FAIRRING_NVLS": "off"},
@@ -235,8 +237,10 @@ def test_backend_on_gpus(name):
         assert stats["launch_nvls_allreduce"] + stats["launch_nvls_oneshot_allreduce"] > 0
     if name.startswith("pipe") and name != "pipe_off":
         assert stats["launch_pipe_allreduce"] > 0
-    if name == "pipe_off":
+    if name in ("pipe_off", "narrow_in_place"):
         assert stats["launch_pipe_allreduce"] == 0
+    if name == "narrow_in_place" and stats["nvls"] == 1:
+        assert stats["launch_nvls_direct_allreduce"] > 0
     if name == "auto":
         assert stats["launch_pipe_allreduce"] > 0
     if name == "hier_three_kernels":
