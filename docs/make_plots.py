@@ -1,7 +1,7 @@
 """Draws the figures under docs/ from measured sweep rows, as plain SVG (no
 plotting library needed).
 
-    python docs/make_plots.py profiles/data/sweep8_ordinary.json docs/allreduce_busbw_ordinary.svg \\
+    python docs/make_plots.py docs/data/sweep8_fairring_ordinary.json docs/data/sweep8_nccl.json docs/allreduce_busbw_8gpu.svg \\
         --title "all-reduce, 8 x B200, fp32, ordinary tensors"
 
 The input is what ``python -m fairring_b200.bench.sweep --json`` (or
