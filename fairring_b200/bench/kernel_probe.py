@@ -22,7 +22,8 @@ import torch
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="twoshot",
-                    choices=["oneshot", "twoshot", "hier", "direct", "ll", "pipe", "adamw", "sumsq"])
+                    choices=["oneshot", "twoshot", "hier", "direct", "ll", "pipe", "adamw", "sumsq",
+                             "layernorm", "cross_entropy"])
     ap.add_argument("--world", type=int, default=8)
     ap.add_argument("--gpus-per-machine", type=int, default=0, help="hier: group size (default world/2)")
     ap.add_argument("--mib", type=float, default=16.0, help="message (or buffer) size per rank, MiB")
@@ -55,6 +56,37 @@ def main(argv=None) -> int:
             fn = lambda i: C.sumsq(g)  # noqa: E731
             algo_bytes = n * 4
             pattern = "sumsq"
+    elif args.kernel == "layernorm":
+        # the decoder's shape: rows of 2048 bf16 in, bf16 out, fp32 affine parameters
+        cols = 2048
+        rows = max(1, int(args.mib * (1 << 20)) // (2 * cols))
+        x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+        dy = torch.randn_like(x)
+        gamma, beta = torch.ones(cols, device="cuda"), torch.zeros(cols, device="cuda")
+        state = {}
+
+        def fn(i):
+            y, mean, rstd = C.layer_norm_fwd(x, gamma, beta, 1e-5, torch.bfloat16)
+            state["out"] = C.layer_norm_bwd(dy, x, gamma, mean, rstd)
+
+        # forward: read x, write y; backward: read dy and x, write dx (statistics are per row)
+        algo_bytes = rows * cols * 2 * 5
+        pattern = "layer_norm_fwd_kernel|layer_norm_bwd_kernel"
+    elif args.kernel == "cross_entropy":
+        vocab = 51200
+        rows = max(1, int(args.mib * (1 << 20)) // (2 * vocab))
+        logits = torch.randn(rows, vocab, device="cuda", dtype=torch.bfloat16)
+        targets = torch.randint(0, vocab, (rows,), device="cuda")
+        one = torch.ones(1, device="cuda")
+
+        def fn(i):
+            logits.normal_()
+            loss, lse = C.cross_entropy_fwd(logits, targets)
+            C.cross_entropy_bwd_(logits, targets, lse, one, 1.0 / rows)
+
+        # forward: read the logits once (the second sweep of a row hits L2); backward: read + write
+        algo_bytes = rows * vocab * 2 * 3
+        pattern = "cross_entropy_fwd_kernel|cross_entropy_bwd_kernel"
     elif args.kernel == "pipe":
         ins = [torch.randn(n, device="cuda").to(dtype) for _ in range(W)]
         fn = lambda i: C.emulated_pipe_allreduce(  # noqa: E731

@@ -66,9 +66,11 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
   if (cfg_.pipe_blocks > kMaxBlocks) cfg_.pipe_blocks = kMaxBlocks;
   // FAIRRING_SM_BUDGET further limits how many SMs the collectives may hold at
   // once, so that backward keeps most of the GPU while gradients are reduced.
-  const int widest = want_pipe ? std::max(cfg_.blocks, cfg_.pipe_blocks) : cfg_.blocks;
-  const int budget = std::max(widest, std::min(sms, cfg_.sm_budget));
-  const int max_channels = std::max(1, budget / widest);
+  // The budget counts the staged kernels (`blocks` each).  A pipelined launch
+  // may be wider, but only the first pipe_channels channels ever run one, and
+  // large ordinary tensors are not what runs under backward.
+  const int budget = std::max(cfg_.blocks, std::min(sms, cfg_.sm_budget));
+  const int max_channels = std::max(1, budget / cfg_.blocks);
   if (cfg_.parallelism > max_channels) cfg_.parallelism = max_channels;
   // The flag-in-data areas come off the top of the budget (a quarter at most):
   // fewer channels first, then smaller messages.
@@ -112,6 +114,14 @@ Engine::Engine(std::shared_ptr<KvStore> store, const Topo& topo, int device,
 
   if (want_pipe) {
     pipe_channels_ = std::max(1, std::min<int>(cfg_.pipe_channels, plan_.channels));
+    // Residency: every kernel that can be in flight at once must fit on the GPU
+    // (a channel runs one kernel at a time: the wider of the two on a pipe channel).
+    auto resident = [&] {
+      return pipe_channels_ * std::max(cfg_.blocks, cfg_.pipe_blocks) +
+             (plan_.channels - pipe_channels_) * cfg_.blocks;
+    };
+    while (resident() > sms && pipe_channels_ > 1) --pipe_channels_;
+    while (resident() > sms && cfg_.pipe_blocks > cfg_.blocks) --cfg_.pipe_blocks;
     if (cfg_.pipe_slots < 2) cfg_.pipe_slots = 2;
     const int64_t ring_total = rest / 3;
     pipe_slot_bytes_ = roundDown(ring_total / pipe_channels_ / cfg_.pipe_slots, 4096);
