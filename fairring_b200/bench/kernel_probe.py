@@ -57,11 +57,11 @@ def main(argv=None) -> int:
             algo_bytes = n * 4
             pattern = "sumsq"
     elif args.kernel == "layernorm":
-        # the decoder's shape: rows of 2048 bf16 in, bf16 out, fp32 affine parameters
+        # the decoder's shape: rows of 2048 (fp32 residual stream, or bf16) in, bf16 out
         cols = 2048
-        rows = max(1, int(args.mib * (1 << 20)) // (2 * cols))
-        x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
-        dy = torch.randn_like(x)
+        rows = max(1, int(args.mib * (1 << 20)) // (es * cols))
+        x = torch.randn(rows, cols, device="cuda", dtype=dtype)
+        dy = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
         gamma, beta = torch.ones(cols, device="cuda"), torch.zeros(cols, device="cuda")
         state = {}
 
@@ -70,8 +70,8 @@ def main(argv=None) -> int:
             state["out"] = C.layer_norm_bwd(dy, x, gamma, mean, rstd)
 
         # forward: read x, write y; backward: read dy and x, write dx (statistics are per row)
-        algo_bytes = rows * cols * 2 * 5
-        pattern = "layer_norm_fwd_kernel|layer_norm_bwd_kernel"
+        algo_bytes = rows * cols * (3 * es + 2 * 2)
+        pattern = "layer_norm_fwd_kernel|layer_norm_bwd_kernel|layer_norm_param_grad_kernel"
     elif args.kernel == "cross_entropy":
         vocab = 51200
         rows = max(1, int(args.mib * (1 << 20)) // (2 * vocab))
@@ -126,18 +126,21 @@ def main(argv=None) -> int:
 
     total_us, calls = 0.0, 0
     names = []
+    each = {}
     for e in prof.key_averages():
         if re.search(pattern, e.key):
             total_us += e.device_time_total
             calls = max(calls, e.count)
             names.append(e.key[:80])
+            short = re.sub(r"<.*", "", e.key.split("::")[-1])
+            each[short] = round(each.get(short, 0.0) + e.device_time_total / max(1, args.iters), 1)
     per_call_us = total_us / max(1, args.iters)
     print(json.dumps({
         "kernel": args.kernel, "world": W, "bytes_per_rank": n * es, "dtype": args.dtype,
         "blocks_per_rank": args.blocks, "device_us_per_call": round(per_call_us, 1),
         "algorithmic_hbm_bytes": int(algo_bytes),
         "achieved_gbs": round(algo_bytes / (per_call_us * 1e-6) / 1e9, 1) if per_call_us else None,
-        "kernels": names,
+        "us_per_kernel": each, "kernels": names,
     }))
     return 0
 

@@ -77,7 +77,7 @@ __device__ __forceinline__ float2 blockSum2(float a, float b, float2* scratch) {
 }
 
 template <typename TX, typename TY, int ITER>
-__global__ void __launch_bounds__(kLnThreads)
+__global__ void __launch_bounds__(kLnThreads, ITER == 1 ? 8 : 1)
 layer_norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ gamma,
                       const float* __restrict__ beta, TY* __restrict__ y, float* __restrict__ mean_out,
                       float* __restrict__ rstd_out, int64_t rows, int cols, float eps) {
@@ -123,19 +123,17 @@ layer_norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ gamma,
 // dx for the rows of this block, plus this block's partial sums of the weight
 // and bias gradients: partial[block][0][col] = sum dy * xhat, [block][1][col] = sum dy.
 template <typename TX, typename TY, int ITER>
-__global__ void __launch_bounds__(kLnThreads)
+__global__ void __launch_bounds__(kLnThreads, ITER == 1 ? 4 : 1)
 layer_norm_bwd_kernel(const TY* __restrict__ dy, const TX* __restrict__ x,
                       const float* __restrict__ gamma, const float* __restrict__ mean_in,
                       const float* __restrict__ rstd_in, TX* __restrict__ dx,
                       float* __restrict__ partial, int64_t rows, int cols) {
   __shared__ float2 scratch[kLnThreads / 32];
-  float dg[ITER][8], db[ITER][8], g[ITER][8];
+  float dg[ITER][8], db[ITER][8];
 #pragma unroll
   for (int it = 0; it < ITER; ++it) {
-    const int c = (it * kLnThreads + threadIdx.x) * 8;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) dg[it][i] = db[it][i] = g[it][i] = 0.f;
-    if (c < cols) load8<float>(gamma + c, g[it]);
+    for (int i = 0; i < 8; ++i) dg[it][i] = db[it][i] = 0.f;
   }
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     const float mean = mean_in[r], rstd = rstd_in[r];
@@ -145,13 +143,14 @@ layer_norm_bwd_kernel(const TY* __restrict__ dy, const TX* __restrict__ x,
     for (int it = 0; it < ITER; ++it) {
       const int c = (it * kLnThreads + threadIdx.x) * 8;
       if (c < cols) {
-        float xv[8], dv[8];
+        float xv[8], dv[8], gv[8];
         load8<TX>(x + r * cols + c, xv);
         load8<TY>(dy + r * cols + c, dv);
+        load8<float>(gamma + c, gv);  // stays in L1: keeping it in registers costs a block of occupancy
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           xh[it][i] = (xv[i] - mean) * rstd;
-          w[it][i] = dv[i] * g[it][i];
+          w[it][i] = dv[i] * gv[i];
           s1 += w[it][i];
           s2 += w[it][i] * xh[it][i];
           dg[it][i] += dv[i] * xh[it][i];
@@ -183,18 +182,39 @@ layer_norm_bwd_kernel(const TY* __restrict__ dy, const TX* __restrict__ x,
   }
 }
 
-// dgamma[c] = sum over blocks of partial[b][0][c]; dbeta likewise.
+// dgamma[c] = sum over blocks of partial[b][0][c]; dbeta likewise.  A block of
+// 8 warps owns 32 of the 2 x cols columns: warp w sums partial rows w, w+8, ...
+// (one 128-byte line per load, four loads in flight), then the warps' sums
+// are added through shared memory.
 __global__ void __launch_bounds__(256)
 layer_norm_param_grad_kernel(const float* __restrict__ partial, int nblocks, int cols,
                              float* __restrict__ dgamma, float* __restrict__ dbeta) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * cols) return;
-  float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[(size_t)b * 2 * cols + c];
-  if (c < cols)
-    dgamma[c] = s;
-  else
-    dbeta[c - cols] = s;
+  __shared__ float acc[8][33];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  const size_t stride = (size_t)2 * cols;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (c < 2 * cols) {
+    int b = w;
+    for (; b + 24 < nblocks; b += 32) {
+      s0 += partial[(size_t)b * stride + c];
+      s1 += partial[(size_t)(b + 8) * stride + c];
+      s2 += partial[(size_t)(b + 16) * stride + c];
+      s3 += partial[(size_t)(b + 24) * stride + c];
+    }
+    for (; b < nblocks; b += 8) s0 += partial[(size_t)b * stride + c];
+  }
+  acc[w][lane] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (w == 0 && c < 2 * cols) {
+    float s = acc[0][lane];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) s += acc[i][lane];
+    if (c < cols)
+      dgamma[c] = s;
+    else
+      dbeta[c - cols] = s;
+  }
 }
 
 template <typename TX, typename TY>
@@ -276,7 +296,7 @@ cudaError_t launchLayerNormBackward(const void* dy, bool y_bf16, const void* x, 
     e = y_bf16 ? bwdDispatch<float, __nv_bfloat16>(dy, x, gamma, mean, rstd, dx, partial, rows, cols, blocks, stream)
                : bwdDispatch<float, float>(dy, x, gamma, mean, rstd, dx, partial, rows, cols, blocks, stream);
   if (e != cudaSuccess) return e;
-  layer_norm_param_grad_kernel<<<(2 * cols + 255) / 256, 256, 0, stream>>>(partial, blocks, cols, dgamma, dbeta);
+  layer_norm_param_grad_kernel<<<(2 * cols + 31) / 32, 256, 0, stream>>>(partial, blocks, cols, dgamma, dbeta);
   noteLocalLaunch();
   noteLocalLaunch();
   return cudaGetLastError();
