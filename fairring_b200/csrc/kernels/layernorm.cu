@@ -217,6 +217,170 @@ layer_norm_param_grad_kernel(const float* __restrict__ partial, int nblocks, int
   }
 }
 
+// ---- residual add + LayerNorm ---------------------------------------------------
+// xnew = x + branch (the fp32 residual stream plus a block's output, bf16 under
+// autocast), y = LayerNorm(xnew).  A separate add reads and writes the stream
+// once more per LayerNorm; here the sum is formed in the registers that the
+// statistics are computed from.
+template <typename TB, typename TY, int ITER>
+__global__ void __launch_bounds__(kLnThreads, ITER == 1 ? 6 : 1)
+add_layer_norm_fwd_kernel(const float* __restrict__ x, const TB* __restrict__ branch,
+                          const float* __restrict__ gamma, const float* __restrict__ beta,
+                          float* __restrict__ xnew, TY* __restrict__ y, float* __restrict__ mean_out,
+                          float* __restrict__ rstd_out, int64_t rows, int cols, float eps) {
+  __shared__ float2 scratch[kLnThreads / 32];
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    float v[ITER][8];
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const int c = (it * kLnThreads + threadIdx.x) * 8;
+      if (c < cols) {
+        float b[8];
+        load8<float>(x + r * cols + c, v[it]);
+        load8<TB>(branch + r * cols + c, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          v[it][i] += b[i];
+          s += v[it][i];
+          ss += v[it][i] * v[it][i];
+        }
+        store8<float>(xnew + r * cols + c, v[it]);
+      }
+    }
+    const float2 t = blockSum2(s, ss, scratch);
+    const float mean = t.x / cols;
+    const float var = fmaxf(t.y / cols - mean * mean, 0.f);
+    const float rstd = rsqrtf(var + eps);
+    if (threadIdx.x == 0) {
+      mean_out[r] = mean;
+      rstd_out[r] = rstd;
+    }
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const int c = (it * kLnThreads + threadIdx.x) * 8;
+      if (c < cols) {
+        float g[8], b[8], o[8];
+        load8<float>(gamma + c, g);
+        load8<float>(beta + c, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = (v[it][i] - mean) * rstd * g[i] + b[i];
+        store8<TY>(y + r * cols + c, o);
+      }
+    }
+  }
+}
+
+// dx = LayerNorm backward of dy at xnew, plus `gres`, the gradient that reaches
+// xnew along the residual path (null: none).  dx is the gradient of both
+// addends; `dbranch` (null: not wanted) receives it in bf16 for a bf16 branch.
+template <typename TY, int ITER>
+__global__ void __launch_bounds__(kLnThreads, ITER == 1 ? 4 : 1)
+add_layer_norm_bwd_kernel(const TY* __restrict__ dy, const float* __restrict__ xnew,
+                          const float* __restrict__ gres, const float* __restrict__ gamma,
+                          const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                          float* __restrict__ dx, __nv_bfloat16* __restrict__ dbranch,
+                          float* __restrict__ partial, int64_t rows, int cols) {
+  __shared__ float2 scratch[kLnThreads / 32];
+  float dg[ITER][8], db[ITER][8];
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dg[it][i] = db[it][i] = 0.f;
+  }
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float mean = mean_in[r], rstd = rstd_in[r];
+    float xh[ITER][8], w[ITER][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const int c = (it * kLnThreads + threadIdx.x) * 8;
+      if (c < cols) {
+        float xv[8], dv[8], gv[8];
+        load8<float>(xnew + r * cols + c, xv);
+        load8<TY>(dy + r * cols + c, dv);
+        load8<float>(gamma + c, gv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[it][i] = (xv[i] - mean) * rstd;
+          w[it][i] = dv[i] * gv[i];
+          s1 += w[it][i];
+          s2 += w[it][i] * xh[it][i];
+          dg[it][i] += dv[i] * xh[it][i];
+          db[it][i] += dv[i];
+        }
+      }
+    }
+    const float2 t = blockSum2(s1, s2, scratch);
+    const float m1 = t.x / cols, m2 = t.y / cols;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const int c = (it * kLnThreads + threadIdx.x) * 8;
+      if (c < cols) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (w[it][i] - m1 - xh[it][i] * m2);
+        if (gres != nullptr) {
+          float gr[8];
+          load8<float>(gres + r * cols + c, gr);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += gr[i];
+        }
+        store8<float>(dx + r * cols + c, o);
+        if (dbranch != nullptr) store8<__nv_bfloat16>(dbranch + r * cols + c, o);
+      }
+    }
+  }
+  float* p = partial + (size_t)blockIdx.x * 2 * cols;
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+    const int c = (it * kLnThreads + threadIdx.x) * 8;
+    if (c < cols) {
+      store8<float>(p + c, dg[it]);
+      store8<float>(p + cols + c, db[it]);
+    }
+  }
+}
+
+template <typename TB, typename TY>
+cudaError_t addFwdDispatch(const float* x, const void* branch, const float* gamma, const float* beta,
+                           float* xnew, void* y, float* mean, float* rstd, int64_t rows, int cols,
+                           float eps, int blocks, cudaStream_t s) {
+  const int iter = (cols / 8 + kLnThreads - 1) / kLnThreads;
+#define FR_ALN_FWD(I)                                                                         \
+  add_layer_norm_fwd_kernel<TB, TY, I><<<blocks, kLnThreads, 0, s>>>(                          \
+      x, static_cast<const TB*>(branch), gamma, beta, xnew, static_cast<TY*>(y), mean, rstd, rows, cols, eps)
+  switch (iter) {
+    case 1: FR_ALN_FWD(1); break;
+    case 2: FR_ALN_FWD(2); break;
+    case 3: FR_ALN_FWD(3); break;
+    case 4: FR_ALN_FWD(4); break;
+    default: return cudaErrorInvalidValue;
+  }
+#undef FR_ALN_FWD
+  return cudaGetLastError();
+}
+
+template <typename TY>
+cudaError_t addBwdDispatch(const void* dy, const float* xnew, const float* gres, const float* gamma,
+                           const float* mean, const float* rstd, float* dx, void* dbranch,
+                           float* partial, int64_t rows, int cols, int blocks, cudaStream_t s) {
+  const int iter = (cols / 8 + kLnThreads - 1) / kLnThreads;
+#define FR_ALN_BWD(I)                                                                         \
+  add_layer_norm_bwd_kernel<TY, I><<<blocks, kLnThreads, 0, s>>>(                              \
+      static_cast<const TY*>(dy), xnew, gres, gamma, mean, rstd, dx,                           \
+      static_cast<__nv_bfloat16*>(dbranch), partial, rows, cols)
+  switch (iter) {
+    case 1: FR_ALN_BWD(1); break;
+    case 2: FR_ALN_BWD(2); break;
+    case 3: FR_ALN_BWD(3); break;
+    case 4: FR_ALN_BWD(4); break;
+    default: return cudaErrorInvalidValue;
+  }
+#undef FR_ALN_BWD
+  return cudaGetLastError();
+}
+
 template <typename TX, typename TY>
 cudaError_t fwdDispatch(const void* x, const float* gamma, const float* beta, void* y, float* mean,
                         float* rstd, int64_t rows, int cols, float eps, int blocks, cudaStream_t s) {
@@ -295,6 +459,42 @@ cudaError_t launchLayerNormBackward(const void* dy, bool y_bf16, const void* x, 
   else
     e = y_bf16 ? bwdDispatch<float, __nv_bfloat16>(dy, x, gamma, mean, rstd, dx, partial, rows, cols, blocks, stream)
                : bwdDispatch<float, float>(dy, x, gamma, mean, rstd, dx, partial, rows, cols, blocks, stream);
+  if (e != cudaSuccess) return e;
+  layer_norm_param_grad_kernel<<<(2 * cols + 31) / 32, 256, 0, stream>>>(partial, blocks, cols, dgamma, dbeta);
+  noteLocalLaunch();
+  noteLocalLaunch();
+  return cudaGetLastError();
+}
+
+cudaError_t launchAddLayerNormForward(const float* x, const void* branch, bool branch_bf16,
+                                      const float* gamma, const float* beta, float* xnew, void* y,
+                                      bool y_bf16, float* mean, float* rstd, int64_t rows, int cols,
+                                      float eps, int sm_count, cudaStream_t stream) {
+  if (rows <= 0) return cudaSuccess;
+  if (cols % 8 != 0 || cols > 8192) return cudaErrorInvalidValue;
+  int64_t blocks = (int64_t)sm_count * 6;
+  if (blocks > rows) blocks = rows;
+  cudaError_t e;
+  if (branch_bf16)
+    e = y_bf16 ? addFwdDispatch<__nv_bfloat16, __nv_bfloat16>(x, branch, gamma, beta, xnew, y, mean, rstd, rows, cols, eps, (int)blocks, stream)
+               : addFwdDispatch<__nv_bfloat16, float>(x, branch, gamma, beta, xnew, y, mean, rstd, rows, cols, eps, (int)blocks, stream);
+  else
+    e = y_bf16 ? addFwdDispatch<float, __nv_bfloat16>(x, branch, gamma, beta, xnew, y, mean, rstd, rows, cols, eps, (int)blocks, stream)
+               : addFwdDispatch<float, float>(x, branch, gamma, beta, xnew, y, mean, rstd, rows, cols, eps, (int)blocks, stream);
+  noteLocalLaunch();
+  return e;
+}
+
+cudaError_t launchAddLayerNormBackward(const void* dy, bool y_bf16, const float* xnew, const float* gres,
+                                       const float* gamma, const float* mean, const float* rstd,
+                                       float* dx, void* dbranch_bf16, float* partial, float* dgamma,
+                                       float* dbeta, int64_t rows, int cols, int sm_count,
+                                       cudaStream_t stream) {
+  if (rows <= 0) return cudaSuccess;
+  if (cols % 8 != 0 || cols > 8192) return cudaErrorInvalidValue;
+  const int blocks = layerNormBackwardBlocks(rows, sm_count);
+  cudaError_t e = y_bf16 ? addBwdDispatch<__nv_bfloat16>(dy, xnew, gres, gamma, mean, rstd, dx, dbranch_bf16, partial, rows, cols, blocks, stream)
+                         : addBwdDispatch<float>(dy, xnew, gres, gamma, mean, rstd, dx, dbranch_bf16, partial, rows, cols, blocks, stream);
   if (e != cudaSuccess) return e;
   layer_norm_param_grad_kernel<<<(2 * cols + 31) / 32, 256, 0, stream>>>(partial, blocks, cols, dgamma, dbeta);
   noteLocalLaunch();

@@ -46,6 +46,20 @@ cudaError_t launchLayerNormBackward(const void* dy, bool y_bf16, const void* x, 
                                     float* partial, float* dgamma, float* dbeta, int64_t rows, int cols,
                                     int sm_count, cudaStream_t stream);
 
+// xnew = x + branch (x fp32, branch fp32 or bf16), y = LayerNorm(xnew); the
+// backward adds `gres` (gradient arriving at xnew along the residual path, may
+// be null) to the LayerNorm gradient and can also write the sum in bf16
+// (`dbranch_bf16`, may be null).
+cudaError_t launchAddLayerNormForward(const float* x, const void* branch, bool branch_bf16,
+                                      const float* gamma, const float* beta, float* xnew, void* y,
+                                      bool y_bf16, float* mean, float* rstd, int64_t rows, int cols,
+                                      float eps, int sm_count, cudaStream_t stream);
+cudaError_t launchAddLayerNormBackward(const void* dy, bool y_bf16, const float* xnew, const float* gres,
+                                       const float* gamma, const float* mean, const float* rstd,
+                                       float* dx, void* dbranch_bf16, float* partial, float* dgamma,
+                                       float* dbeta, int64_t rows, int cols, int sm_count,
+                                       cudaStream_t stream);
+
 // Softmax cross-entropy over [rows, vocab] logits (fp32 or bf16, vocab a
 // multiple of 8): per-row loss and log-sum-exp; the backward overwrites the
 // logits with their gradient, scaled by *upstream (a device scalar) * scale.

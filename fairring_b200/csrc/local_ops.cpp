@@ -7,6 +7,7 @@
 #include <torch/extension.h>
 
 #include <cmath>
+#include <optional>
 #include <tuple>
 
 #include "kernels/local_kernels.h"
@@ -131,6 +132,73 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> layerNormBackward(at::Tensor dy, 
   return std::make_tuple(dx, dgamma, dbeta);
 }
 
+// xnew, y, mean, rstd = x + branch, layer_norm(x + branch); x fp32, branch fp32 or bf16.
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> addLayerNormForward(
+    at::Tensor x, at::Tensor branch, at::Tensor gamma, at::Tensor beta, double eps,
+    at::ScalarType out_dtype) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == at::kFloat && x.dim() >= 1,
+              "x must be a contiguous fp32 CUDA tensor");
+  TORCH_CHECK(branch.is_cuda() && branch.is_contiguous() && branch.sizes() == x.sizes() &&
+                  (branch.scalar_type() == at::kFloat || branch.scalar_type() == at::kBFloat16),
+              "branch must be contiguous, shaped like x, fp32 or bf16");
+  TORCH_CHECK(out_dtype == at::kFloat || out_dtype == at::kBFloat16, "output must be fp32 or bf16");
+  const int64_t cols = x.size(-1);
+  const int64_t rows = x.numel() / std::max<int64_t>(cols, 1);
+  TORCH_CHECK(gamma.is_cuda() && beta.is_cuda() && gamma.scalar_type() == at::kFloat &&
+                  beta.scalar_type() == at::kFloat && gamma.is_contiguous() && beta.is_contiguous() &&
+                  gamma.numel() == cols && beta.numel() == cols,
+              "weight and bias must be contiguous fp32 CUDA vectors of the row length");
+  TORCH_CHECK(cols % 8 == 0 && cols <= 8192, "row length must be a multiple of 8, at most 8192");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor xnew = at::empty_like(x);
+  at::Tensor y = at::empty(x.sizes(), x.options().dtype(out_dtype));
+  at::Tensor mean = at::empty({rows}, x.options());
+  at::Tensor rstd = at::empty({rows}, x.options());
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  cudaError_t e = launchAddLayerNormForward(
+      x.data_ptr<float>(), branch.data_ptr(), branch.scalar_type() == at::kBFloat16, gamma.data_ptr<float>(),
+      beta.data_ptr<float>(), xnew.data_ptr<float>(), y.data_ptr(), out_dtype == at::kBFloat16,
+      mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, (int)cols, (float)eps, sms,
+      c10::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "add_layer_norm forward launch failed: ", cudaGetErrorString(e));
+  return std::make_tuple(xnew, y, mean, rstd);
+}
+
+// dx (fp32), dx in bf16 (or an undefined tensor), dgamma, dbeta.  `gres`: the
+// gradient that reaches xnew along the residual path, or nothing.
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> addLayerNormBackward(
+    at::Tensor dy, at::Tensor xnew, at::Tensor gamma, at::Tensor mean, at::Tensor rstd,
+    std::optional<at::Tensor> gres, bool want_bf16) {
+  TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && xnew.is_contiguous() && dy.sizes() == xnew.sizes() &&
+                  xnew.scalar_type() == at::kFloat,
+              "dy and xnew must be contiguous and equally shaped, xnew fp32");
+  TORCH_CHECK(dy.scalar_type() == at::kFloat || dy.scalar_type() == at::kBFloat16, "dy must be fp32 or bf16");
+  const float* gres_ptr = nullptr;
+  if (gres.has_value() && gres->defined()) {
+    TORCH_CHECK(gres->is_cuda() && gres->is_contiguous() && gres->scalar_type() == at::kFloat &&
+                    gres->sizes() == xnew.sizes(),
+                "the residual gradient must be contiguous fp32, shaped like xnew");
+    gres_ptr = gres->data_ptr<float>();
+  }
+  const int64_t cols = xnew.size(-1);
+  const int64_t rows = xnew.numel() / std::max<int64_t>(cols, 1);
+  c10::cuda::CUDAGuard guard(xnew.device());
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  at::Tensor dx = at::empty_like(xnew);
+  at::Tensor dbr;
+  if (want_bf16) dbr = at::empty(xnew.sizes(), xnew.options().dtype(at::kBFloat16));
+  at::Tensor dgamma = at::empty({cols}, gamma.options());
+  at::Tensor dbeta = at::empty({cols}, gamma.options());
+  at::Tensor partial = at::empty({(int64_t)layerNormBackwardBlocks(rows, sms), 2, cols}, gamma.options());
+  cudaError_t e = launchAddLayerNormBackward(
+      dy.data_ptr(), dy.scalar_type() == at::kBFloat16, xnew.data_ptr<float>(), gres_ptr,
+      gamma.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), dx.data_ptr<float>(),
+      want_bf16 ? dbr.data_ptr() : nullptr, partial.data_ptr<float>(), dgamma.data_ptr<float>(),
+      dbeta.data_ptr<float>(), rows, (int)cols, sms, c10::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "add_layer_norm backward launch failed: ", cudaGetErrorString(e));
+  return std::make_tuple(dx, dbr, dgamma, dbeta);
+}
+
 // (per-row loss, per-row log-sum-exp) of logits [rows, vocab] against targets [rows].
 std::tuple<at::Tensor, at::Tensor> crossEntropyForward(at::Tensor logits, at::Tensor targets) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous(),
@@ -182,6 +250,10 @@ void bindLocalOps(pybind11::module_& m) {
   m.def("cross_entropy_fwd", &crossEntropyForward, py::arg("logits"), py::arg("targets"));
   m.def("cross_entropy_bwd_", &crossEntropyBackward, py::arg("logits"), py::arg("targets"),
         py::arg("lse"), py::arg("upstream"), py::arg("scale"));
+  m.def("add_layer_norm_fwd", &addLayerNormForward, py::arg("x"), py::arg("branch"), py::arg("weight"),
+        py::arg("bias"), py::arg("eps"), py::arg("out_dtype"));
+  m.def("add_layer_norm_bwd", &addLayerNormBackward, py::arg("dy"), py::arg("xnew"), py::arg("weight"),
+        py::arg("mean"), py::arg("rstd"), py::arg("gres"), py::arg("want_bf16"));
   m.def("layer_norm_fwd", &layerNormForward, py::arg("x"), py::arg("weight"), py::arg("bias"),
         py::arg("eps"), py::arg("out_dtype"));
   m.def("layer_norm_bwd", &layerNormBackward, py::arg("dy"), py::arg("x"), py::arg("weight"),

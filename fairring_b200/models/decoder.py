@@ -25,6 +25,7 @@ class DecoderConfig:
     seq_len: int = 1024
     fused_norm: bool = True  # one-kernel LayerNorm on the GPU (fairring_b200.ops.FusedLayerNorm)
     fused_loss: bool = True  # two-kernel cross-entropy on the GPU (fairring_b200.ops.fused_cross_entropy)
+    fused_residual: bool = True  # residual add inside the next LayerNorm's kernels (fairring_b200.ops.add_layer_norm)
 
     @staticmethod
     def flagship() -> "DecoderConfig":
@@ -65,6 +66,22 @@ class Block(nn.Module):
         x = x + self.fc2(F.gelu(self.fc1(self.ln2(x)), approximate="tanh"))
         return x
 
+    def forward_pending(self, x: torch.Tensor, pending: torch.Tensor | None):
+        """The same block with every residual add moved into the LayerNorm that
+        follows it: takes the stream and the output of the block before that is
+        still to be added to it, returns the stream and this block's own
+        pending output."""
+        from ..ops import add_layer_norm
+
+        b, s, d = x.shape
+        x, h = add_layer_norm(self.ln1, x, pending)
+        q, k, v = self.qkv(h).view(b, s, 3, self.n_head, d // self.n_head).unbind(2)
+        a = F.scaled_dot_product_attention(
+            q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True
+        )
+        x, h = add_layer_norm(self.ln2, x, self.proj(a.transpose(1, 2).reshape(b, s, d)))
+        return x, self.fc2(F.gelu(self.fc1(h), approximate="tanh"))
+
 
 class DecoderLM(nn.Module):
     def __init__(self, cfg: DecoderConfig):
@@ -94,9 +111,17 @@ class DecoderLM(nn.Module):
         b, s = tokens.shape
         pos = torch.arange(s, device=tokens.device)
         x = self.tok(tokens) + self.pos(pos)
-        for blk in self.blocks:
-            x = blk(x)
-        x = self.ln_f(x)
+        if self.cfg.fused_residual and self.cfg.fused_norm and x.is_cuda and x.dtype == torch.float32:
+            from ..ops import add_layer_norm
+
+            pending = None
+            for blk in self.blocks:
+                x, pending = blk.forward_pending(x, pending)
+            _, x = add_layer_norm(self.ln_f, x, pending)
+        else:
+            for blk in self.blocks:
+                x = blk(x)
+            x = self.ln_f(x)
         logits = F.linear(x, self.tok.weight)  # tied output embedding
         if targets is None:
             return logits

@@ -83,3 +83,16 @@ def test_fused_ops_fall_back_off_the_gpu():
     torch.testing.assert_close(loss.detach(), ref)
     loss.backward()
     assert float(logits.grad[3].abs().sum()) == 0.0
+
+
+def test_block_with_pending_residual_equals_plain_block_on_cpu():
+    from fairring_b200.models import DecoderConfig, DecoderLM
+
+    torch.manual_seed(1)
+    m = DecoderLM(DecoderConfig.tiny())
+    x = torch.randn(2, 64, 128)
+    pend = torch.randn(2, 64, 128) * 0.1
+    blk = m.blocks[0]
+    ref = blk(x + pend)
+    xs, out = blk.forward_pending(x, pend)
+    torch.testing.assert_close(xs + out, ref, rtol=1e-5, atol=1e-5)
