@@ -47,11 +47,13 @@ FAIRRING_PIPE                  auto | on | off: ordinary tensors of FAIRRING_PIP
                                take the pipelined kernel (bulk copy in, switch reduce, bulk copy
                                out, chunk by chunk in one launch); its staging rings take a third
                                of the memory budget
-FAIRRING_PIPE_MIN              smallest message (bytes) for the pipelined kernel (default 512 KiB)
+FAIRRING_PIPE_MIN              smallest message (bytes) for the pipelined kernel (default 64 MiB; it
+                               also needs ring slots of 4 MiB or more, i.e. a memory budget of
+                               about 100 MiB, below which the staged kernels serve)
 FAIRRING_PIPE_BLOCKS           thread blocks of a pipelined launch (default 16)
 FAIRRING_PIPE_CHANNELS         rings, i.e. pipelined launches that may overlap (default 2)
 FAIRRING_PIPE_SLOTS            ring length in chunks (default 4)
-FAIRRING_PIPE_CHUNK            chunk bytes (default: from the message size)
+FAIRRING_PIPE_CHUNK            chunk bytes (default: 16 MiB or the ring slot, whichever is smaller)
 FAIRRING_PIPE_STAGE / _STAGES  shared-memory stage bytes / stages per copy role (16 KiB x 6)
 FAIRRING_DIRECT_MAX_SLICES     in-place NVLS messages are split over at most this many channels
 FAIRRING_DIRECT_MIN_SLICE      ... down to slices of this many bytes

@@ -193,7 +193,7 @@ def main(argv=None) -> int:
                 add("small", {"variant": name}, size, us, bw)
             arena.normal_()
         setopt(algo=ALGO["auto"], ll_max_bytes=32 << 10, ll2_max_bytes=1 << 20, inline_small=1,
-               pipe_min_bytes=512 << 10)
+               pipe_min_bytes=64 << 20)
         be.check_health()
 
     if rank == 0:

@@ -64,7 +64,7 @@ struct OptionsFairring : c10d::Backend::Options {
   std::string transport = "auto";  // auto | vmm | ipc
   std::string direct = "auto";     // auto | p2p | nvls | off: in-place path for symmetric tensors
   std::string pipe = "auto";       // auto | on | off: pipelined kernel for ordinary tensors
-  int64_t pipe_min_bytes = 512 << 10;
+  int64_t pipe_min_bytes = 64 << 20;
   int64_t pipe_blocks = 16;
   int64_t pipe_channels = 2;
   int64_t pipe_slots = 4;

@@ -510,6 +510,9 @@ bool Engine::runPipe(const CollectiveDesc& d, const std::function<Channel&(int)>
   // The threshold was measured with the configured chunk: without room for it
   // in the ring the staged kernels are the better choice.
   if (!forced && cfg_.pipe_chunk_bytes > pipe_slot_bytes_) return false;
+  // Every chunk costs a fixed 13-15 us of publication fences (8 GPUs): with
+  // slots under 4 MiB the kernel cannot amortise them.
+  if (!forced && pipe_slot_bytes_ < (4ll << 20)) return false;
   if (((reinterpret_cast<uintptr_t>(d.in) | reinterpret_cast<uintptr_t>(d.out)) & 15u) != 0)
     return false;  // bulk copies need 16-byte aligned addresses
   const int W = topo_.world;
@@ -518,12 +521,16 @@ bool Engine::runPipe(const CollectiveDesc& d, const std::function<Channel&(int)>
   // Small messages: fewer blocks, so that a block's piece of a sub-chunk stays
   // worth a bulk copy (8 KiB or more).
   int blocks = (int)std::min<int64_t>(cfg_.pipe_blocks, std::max<int64_t>(1, bytes / ((int64_t)W * 8192)));
-  // Chunk: the whole message when it is small; otherwise an eighth of it,
-  // between 512 KiB and a ring slot.
+  // Chunk, when none is configured: 16 MiB (or the slot, if smaller) for the
+  // large messages that come here by themselves; when the kernel is forced on a
+  // small message, the whole message up to 1 MiB, else an eighth of it.
   const int64_t quantum = (int64_t)kVecBytes * W * blocks;
   int64_t chunk = cfg_.pipe_chunk_bytes;
   if (chunk <= 0) {
-    chunk = bytes <= (1 << 20) ? bytes : std::max<int64_t>(512 << 10, bytes / 8);
+    if (!forced)
+      chunk = 16ll << 20;
+    else
+      chunk = bytes <= (1 << 20) ? bytes : std::max<int64_t>(512 << 10, bytes / 8);
   }
   chunk = roundUp(chunk, quantum);
   if (chunk > pipe_slot_bytes_) chunk = roundDown(pipe_slot_bytes_, kVecBytes);

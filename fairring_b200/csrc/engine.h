@@ -76,7 +76,7 @@ struct EngineConfig {
   // "auto" | "on" | "off".  A third of the memory budget becomes its staging
   // rings when it is enabled.
   std::string pipe = "auto";
-  int64_t pipe_min_bytes = 512 << 10;
+  int64_t pipe_min_bytes = 64 << 20;  // 8 GPUs: ahead of the staged kernels from 64 MiB on
   int32_t pipe_blocks = 16;        // thread blocks of one pipelined launch (fewer for small messages)
   int32_t pipe_channels = 2;       // rings, i.e. pipelined launches that may overlap
   int32_t pipe_slots = 4;          // ring length in chunks
