@@ -96,3 +96,21 @@ def test_block_with_pending_residual_equals_plain_block_on_cpu():
     ref = blk(x + pend)
     xs, out = blk.forward_pending(x, pend)
     torch.testing.assert_close(xs + out, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_plots_are_drawn_from_the_committed_sweep_data(tmp_path):
+    import importlib.util
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    spec = importlib.util.spec_from_file_location("make_plots", root / "docs" / "make_plots.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    out = tmp_path / "busbw.svg"
+    data = root / "docs" / "data"
+    rc = mod.main([str(data / "sweep8_fairring_ordinary.json"), str(data / "sweep8_nccl.json"), str(out),
+                   "--dtype", "fp32", "--min-bytes", str(1 << 20)])
+    assert rc == 0
+    svg = out.read_text()
+    assert svg.startswith("<svg") and svg.count("<path") == 2  # one line per backend
+    assert "1 GiB" in svg
