@@ -1,5 +1,6 @@
-"""The measured-threshold table: how bench/tune.py derives it from rows and how
-the package applies it (no GPU needed)."""
+"""Host-side Python pieces that need no GPU: the measured-threshold table (how
+bench/tune.py derives it and how the package applies it), the off-GPU fallbacks
+of the fused ops, the block with pending residual, the figures."""
 
 import importlib
 import json
